@@ -6,7 +6,7 @@ of mlx-lm (mlx_lm/models/cache.py:325-407, 921-1139) and, for state of fixed
 size, its ``ArraysCache`` (:594-733).
 
 Groups.  Caches (one per block that has one) with equal needs — the same
-number of key/value heads, head size and window — form a *group*.  A group
+number of key/value heads, head size, window and kept first positions — form a *group*.  A group
 has its own pool of pages ``[caches in group, n_pages, heads, page, head_dim]``
 for K and for V, its own free list and, per request, its own block table:
 logical page ``p // page`` of the request -> page id, or -1 where the request
@@ -220,6 +220,10 @@ class CacheManager:
             first_key = max(first_key, length // spec.chunk * spec.chunk)
         return first_key // self.page_size
 
+    def _kept_pages(self, spec: PagedKVSpec) -> int:
+        """Logical pages at the start of a sequence that a window never lets go (they hold kept first positions)."""
+        return (spec.keep_first + self.page_size - 1) // self.page_size if spec.keep_first else 0
+
     def pages_needed(self, rid: Hashable, n: int) -> List[int]:
         """New pages per KV group that reserving ``n`` more positions would take."""
         r = self.requests[rid]
@@ -264,7 +268,7 @@ class CacheManager:
             if g.spec.window is None and not g.spec.chunk:
                 continue
             floor = min(self._window_floor(g.spec, r.length), len(r.pages[gi]))
-            for lp in range(floor):
+            for lp in range(self._kept_pages(g.spec), floor):
                 if r.pages[gi][lp] >= 0:
                     g.pool.free(r.pages[gi][lp])
                     r.pages[gi][lp] = -1
@@ -295,7 +299,7 @@ class CacheManager:
         keep = (new_len + self.page_size - 1) // self.page_size
         for gi, g in enumerate(self.kv_groups):
             floor = self._window_floor(g.spec, new_len)
-            if any(p < 0 for p in r.pages[gi][floor:keep]):
+            if any(p < 0 for p in r.pages[gi][floor:keep]) or any(p < 0 for p in r.pages[gi][:min(self._kept_pages(g.spec), keep)]):
                 raise RuntimeError(f"request {rid!r}: pages the window of length {new_len} needs were given back")
             while len(r.pages[gi]) > keep:
                 p = r.pages[gi].pop()

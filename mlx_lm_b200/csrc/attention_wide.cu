@@ -7,13 +7,17 @@
 //   * keys and values of different widths, and values that are a prefix of the key row itself (v_pool may be
 //     k_pool: a cache of latent rows [c | rotated part] read as keys of width Dk and as values of width Dv);
 //   * the visible keys of position p given by a window (p - window < j <= p), by chunks counted from position
-//     0 of the sequence (floor(j / chunk) = floor(p / chunk), j <= p), or both;
-//   * an output gate: head h's output times sigmoid(gate[t, h]).
+//     0 of the sequence (floor(j / chunk) = floor(p / chunk), j <= p), or both; beside a window, the first
+//     `keep_first` positions of the sequence stay visible to every later position (j < keep_first);
+//   * scores bounded by a soft cap: s <- cap * tanh(s / cap), after the scale and before the softmax;
+//   * an output gate: head h's output times sigmoid(gate[t, h]), or, with `gate_cols`, every output column with a
+//     gate of its own, sigmoid(gate[t, h * Dv + d]).
 //
 // The query arrives in float32 (q + t*ldq + h*qhs, Dk values); a key row lies at
 // ((pg*Hkv + c)*page + row)*krs in k_pool, a value row at the same index times vrs in v_pool.
 //
-// A CTA walks the visible keys in blocks of 64 from the first visible one upwards:
+// A CTA walks the visible keys in blocks of 64 from the first visible one upwards (kept first positions that the
+// window has passed come first, in blocks of 64 from position 0):
 //   A  one thread per (key, head): the dot product, times scale               -> raw scores in shared memory
 //   A' (with talk) one thread per (key, head): the mix over heads             -> mixed scores
 //   B  one warp per head: running maximum, weights exp(s - m), running sum, the correction of what was summed
@@ -68,7 +72,7 @@ attention_wide_kernel(const float* q, int ldq, int qhs, const int* __restrict__ 
                       int n_pages, int page, int Hq, int Hkv, int HB, int Dk, int Dv, int krs, int vrs, int window,
                       int chunk, float scale, const float* __restrict__ talk, const T* k_pool, const T* v_pool,
                       const T* gate, int ldg, TO* __restrict__ out, int ldo, int ohs, const int* __restrict__ rows,
-                      int* __restrict__ status) {
+                      int* __restrict__ status, float softcap, int keep_first, int gate_cols) {
   extern __shared__ __align__(16) unsigned char aw_smem[];
   const int DkP = (Dk + 3) & ~3;
   long long* sRow = reinterpret_cast<long long*>(aw_smem);   // [KB] row of the key in head 0 of its page, or -1
@@ -116,8 +120,10 @@ attention_wide_kernel(const float* q, int ldq, int qhs, const int* __restrict__ 
     item_d[i] = it < n_items ? (it - item_h[i] * DvV) * VV : 0;
   }
 
-  for (int j0 = lo; j0 <= p; j0 += AW_KB) {
-    const int nk = min(AW_KB, p - j0 + 1);
+  const int kf = min(keep_first, lo);        // kept first positions that lie before the window
+  int j0 = kf > 0 ? 0 : lo, j_end = kf > 0 ? kf - 1 : p;
+  for (;;) {
+    const int nk = min(AW_KB, j_end - j0 + 1);
     __syncthreads();        // the block before is done with sRow and sP (first pass: sq, sM are written)
     if (tid < AW_KB) {
       long long row = -1;
@@ -159,6 +165,7 @@ attention_wide_kernel(const float* q, int ldq, int qhs, const int* __restrict__ 
           for (int d = 0; d < Dk; ++d) a = fmaf(qh[d], to_f(kp[d]), a);
         }
         s = a * scale;
+        if (softcap > 0.f) s = softcap * tanhf(s / softcap);
       }
       (talk ? sS : sP)[it] = s;
     }
@@ -223,6 +230,12 @@ attention_wide_kernel(const float* q, int ldq, int qhs, const int* __restrict__ 
         }
       }
     }
+    j0 += AW_KB;
+    if (j0 > j_end) {
+      if (j_end == p) break;
+      j0 = lo;             // the kept positions are done: on to the window
+      j_end = p;
+    }
   }
   __syncthreads();
 #pragma unroll
@@ -230,11 +243,16 @@ attention_wide_kernel(const float* q, int ldq, int qhs, const int* __restrict__ 
     if (tid + i * AW_THREADS < n_items) {
       const int hh = item_h[i], h = h0 + hh;
       const float l = sL[hh];
-      float f = l > 0.f ? 1.f / l : 0.f;
-      if (gate) f *= 1.f / (1.f + expf(-to_f(gate[(size_t)t * ldg + h])));
+      const float f = l > 0.f ? 1.f / l : 0.f;
+      float g0 = 1.f, g1 = 1.f;
+      if (gate) {
+        const T* gp = gate + (size_t)t * ldg + (gate_cols ? (size_t)h * Dv + item_d[i] : (size_t)h);
+        g0 = 1.f / (1.f + expf(-to_f(gp[0])));
+        g1 = (VECV && gate_cols) ? 1.f / (1.f + expf(-to_f(gp[1]))) : g0;
+      }
       TO* op = out + (size_t)t * ldo + (size_t)h * ohs + item_d[i];
-      op[0] = from_f<TO>(o[i][0] * f);
-      if (VECV) op[1] = from_f<TO>(o[i][1] * f);
+      op[0] = from_f<TO>(o[i][0] * f * g0);
+      if (VECV) op[1] = from_f<TO>(o[i][1] * f * g1);
     }
   }
 }
@@ -244,7 +262,8 @@ static int aw_launch(const float* q, int ldq, int qhs, const int* positions, con
                      const int* block_table, int max_pages, int n_pages, int page, int Hq, int Hkv, int HB, int Dk,
                      int Dv, int krs, int vrs, int window, int chunk, float scale, const float* talk,
                      const void* k_pool, const void* v_pool, const void* gate, int ldg, void* out, int ldo, int ohs,
-                     const int* rows, int n_tokens, int* status, cudaStream_t stream) {
+                     const int* rows, int n_tokens, int* status, float softcap, int keep_first, int gate_cols,
+                     cudaStream_t stream) {
   constexpr int NK = KVec<T>::N;
   const bool veck = Dk % NK == 0 && krs % NK == 0 && ((uintptr_t)k_pool & 15) == 0;
   const bool vecv = Dv % 2 == 0 && vrs % 2 == 0 && ((uintptr_t)v_pool & (2 * sizeof(T) - 1)) == 0;
@@ -265,7 +284,7 @@ static int aw_launch(const float* q, int ldq, int qhs, const int* positions, con
     }                                                                                                                  \
     launch_pdl(kern, grid, block, smem, stream, q, ldq, qhs, positions, token_req, block_table, max_pages, n_pages,    \
                page, Hq, Hkv, HB, Dk, Dv, krs, vrs, window, chunk, scale, talk, (const T*)k_pool, (const T*)v_pool,    \
-               (const T*)gate, ldg, (TO*)out, ldo, ohs, rows, status);                                                 \
+               (const T*)gate, ldg, (TO*)out, ldo, ohs, rows, status, softcap, keep_first, gate_cols);                 \
   } while (0)
   if (veck && vecv) AW_GO(true, true);
   else if (veck) AW_GO(true, false);
@@ -278,13 +297,15 @@ static int aw_launch(const float* q, int ldq, int qhs, const int* positions, con
 // q: float32 [*, ldq], head h from column h*qhs, Dk values; pools in `dtype` with rows krs / vrs wide; talk: float32
 // [Hq, Hq] or null; gate: `dtype` [*, ldg] (one column per head) or null; out: `dtype`, or float32 if out_f32, head h
 // from column h*ohs, Dv values; rows: int32 [n_tokens] token rows to take, or null for 0..n_tokens-1;
-// window, chunk <= 0: none.
+// window, chunk <= 0: none; softcap <= 0: none; keep_first: positions 0 .. keep_first-1 stay visible beside the window;
+// gate_cols: gate has Hq * Dv columns, one per output column.
 MLXB_EXPORT int mlxb_attention_wide(int dtype, int out_f32, const float* q, int ldq, int qhs, const int* positions,
                                     const int* token_req, const int* block_table, int max_pages, int n_pages, int page,
                                     int Hq, int Hkv, int Dk, int Dv, int krs, int vrs, int window, int chunk,
                                     float scale, const float* talk, const void* k_pool, const void* v_pool,
                                     const void* gate, int ldg, void* out, int ldo, int ohs, const int* rows,
-                                    int n_tokens, int* status, cudaStream_t stream) {
+                                    int n_tokens, int* status, float softcap, int keep_first, int gate_cols,
+                                    cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (page <= 0 || (page & (page - 1)) || Hq <= 0 || Hkv <= 0 || Hq % Hkv || Dk <= 0 || Dv <= 0 || krs < Dk || vrs < Dv ||
       qhs < Dk || ohs < Dv)
@@ -300,14 +321,14 @@ MLXB_EXPORT int mlxb_attention_wide(int dtype, int out_f32, const float* q, int 
   if (dtype == MLXB_F32)
     return aw_launch<float, float>(q, ldq, qhs, positions, token_req, block_table, max_pages, n_pages, page, Hq, Hkv, HB,
                                    Dk, Dv, krs, vrs, window, chunk, scale, talk, k_pool, v_pool, gate, ldg, out, ldo, ohs,
-                                   rows, n_tokens, status, stream);
+                                   rows, n_tokens, status, softcap, keep_first, gate_cols, stream);
   if (dtype == MLXB_BF16 && out_f32)
     return aw_launch<__nv_bfloat16, float>(q, ldq, qhs, positions, token_req, block_table, max_pages, n_pages, page, Hq,
                                            Hkv, HB, Dk, Dv, krs, vrs, window, chunk, scale, talk, k_pool, v_pool, gate,
-                                           ldg, out, ldo, ohs, rows, n_tokens, status, stream);
+                                           ldg, out, ldo, ohs, rows, n_tokens, status, softcap, keep_first, gate_cols, stream);
   if (dtype == MLXB_BF16)
     return aw_launch<__nv_bfloat16, __nv_bfloat16>(q, ldq, qhs, positions, token_req, block_table, max_pages, n_pages,
                                                    page, Hq, Hkv, HB, Dk, Dv, krs, vrs, window, chunk, scale, talk, k_pool,
-                                                   v_pool, gate, ldg, out, ldo, ohs, rows, n_tokens, status, stream);
+                                                   v_pool, gate, ldg, out, ldo, ohs, rows, n_tokens, status, softcap, keep_first, gate_cols, stream);
   return mlxb_fail(MLXB_BAD_DTYPE, "attention (wide): dtype code %d", dtype);
 }

@@ -15,7 +15,10 @@
 // where two buffers fit; warp w takes the scores of keys 8w .. 8w+7 for
 // all 32 rows (S = Q K^T), masked and scaled into shared memory in float32; eight threads a row keep the running
 // maximum and sum and write the weights as bfloat16; warp w then takes every eighth 8-column tile of the values
-// (O = O * corr + P V) in registers.  Masks: causal, a window, runs of `chunk` positions counted from 0.
+// (O = O * corr + P V) in registers.  Masks: causal, a window, runs of `chunk` positions counted from 0; beside a
+// window the first `keep_first` positions stay visible (their blocks, counted from position 0, are walked before the
+// window's).  Scores may be bounded by a soft cap (cap * tanh(s / cap)) before the softmax.  The gate is one number
+// per head or, with `gate_cols`, one per output column.
 #include "common.cuh"
 
 MLXB_DEFINE_LAST_ERROR()
@@ -57,7 +60,8 @@ attention_wide_tc_kernel(const float* q, int ldq, int qhs, const int* __restrict
                          int Dk, int Dv, int DkE, int seg, int n_seg, int krs, int vrs, int shared_v, int window,
                          int chunk, float scale, const float* __restrict__ talk, const __nv_bfloat16* k_pool,
                          const __nv_bfloat16* v_pool, const __nv_bfloat16* gate, int ldg, TO* __restrict__ out, int ldo,
-                         int ohs, int* __restrict__ status, int bps, int n_rel, float* __restrict__ scratch, int nbuf) {
+                         int ohs, int* __restrict__ status, int bps, int n_rel, float* __restrict__ scratch, int nbuf,
+                         float softcap, int keep_first, int gate_cols) {
   constexpr int M = TC_M * MP, THREADS = TC_THREADS * MP;
   extern __shared__ __align__(16) unsigned char tc_smem[];
   const int ldk = DkE + 8, ldv = shared_v ? ldk : Dv + 8;
@@ -83,14 +87,30 @@ attention_wide_tc_kernel(const float* q, int ldq, int qhs, const int* __restrict
   if (chunk > 0 && (pos0 / chunk) * chunk > lo_min) lo_min = (pos0 / chunk) * chunk;
   int p_max = pos0 + nq - 1;
   int j_first = (lo_min / TC_N) * TC_N;
+  // kept first positions: the blocks 0 .. that lie wholly before the window's first block are walked first
+  int kept_end = min((min(keep_first, lo_min) + TC_N - 1) / TC_N * TC_N, j_first);      // a multiple of TC_N
+  int j_start = kept_end > 0 ? 0 : j_first;
   if (bps > 0) {
-    // single rows with their keys split over the CTAs of grid.z: this one takes the blocks bps*za .. bps*za + bps - 1,
-    // counted from position 0, and leaves an unnormalised partial result for the merge kernel
-    const int za = (lo_min / TC_N) / bps + blockIdx.z;
-    if (za * bps * TC_N > p_max) return;                     // a split without keys
-    j_first = max(j_first, za * bps * TC_N);
-    p_max = min(p_max, (za + 1) * bps * TC_N - 1);
+    // single rows with their keys split over the CTAs of grid.z: first the splits of the kept blocks (bps blocks
+    // each, counted from position 0), then those of the window: split z takes the blocks bps*za .. bps*za + bps - 1,
+    // counted from position 0; each leaves an unnormalised partial result for the merge kernel
+    const int kz = (kept_end / TC_N + bps - 1) / bps;
+    if ((int)blockIdx.z < kz) {
+      j_start = blockIdx.z * bps * TC_N;
+      p_max = min(kept_end, j_start + bps * TC_N) - 1;
+      kept_end = p_max + 1;
+      j_first = kept_end;                                    // nothing of the window
+    } else {
+      const int za = (lo_min / TC_N) / bps + (blockIdx.z - kz);
+      if (za * bps * TC_N > p_max) return;                   // a split without keys
+      j_first = max(j_first, za * bps * TC_N);
+      p_max = min(p_max, (za + 1) * bps * TC_N - 1);
+      kept_end = 0;
+      j_start = j_first;
+    }
   }
+  // the block after the one that starts at j0
+  auto next_block = [&](int j0) { const int n = j0 + TC_N; return (n >= kept_end && n < j_first) ? j_first : n; };
   pdl_wait();
   pdl_trigger();
   q = after_wait(q);
@@ -107,7 +127,7 @@ attention_wide_tc_kernel(const float* q, int ldq, int qhs, const int* __restrict
       const int jj = e / per_key, col = (e - jj * per_key) * 8, j = j0 + jj;
       const int c = col / seg, d = col - c * seg;
       const __nv_bfloat16* src = nullptr;
-      if (j >= lo_min && j <= p_max && c < n_seg) {
+      if ((j >= lo_min || j < keep_first) && j <= p_max && c < n_seg) {
         const int lp = j / page;
         const int pg = lp < max_pages ? bt[lp] : -1;
         if (pg >= n_pages) atomicOr(status, MLXB_ST_PAGE_RANGE);
@@ -123,7 +143,7 @@ attention_wide_tc_kernel(const float* q, int ldq, int qhs, const int* __restrict
       for (int e = tid; e < TC_N * per_v; e += THREADS) {
         const int jj = e / per_v, col = (e - jj * per_v) * 8, j = j0 + jj;
         const __nv_bfloat16* src = nullptr;
-        if (j >= lo_min && j <= p_max) {
+        if ((j >= lo_min || j < keep_first) && j <= p_max) {
           const int lp = j / page;
           const int pg = lp < max_pages ? bt[lp] : -1;
           if (pg >= 0 && pg < n_pages) src = v_pool + (((size_t)pg * Hkv + cv) * page + (j % page)) * vrs + col;
@@ -134,7 +154,7 @@ attention_wide_tc_kernel(const float* q, int ldq, int qhs, const int* __restrict
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
-  load_tiles(j_first, 0);
+  load_tiles(j_start, 0);
 
   // ---- queries: float32 -> hi + lo; with talk, the heads' queries mixed into the key heads' segments
   const int rows_used = nq * HG;                             // rows 0 .. rows_used - 1 carry a (token, head)
@@ -181,11 +201,12 @@ attention_wide_tc_kernel(const float* q, int ldq, int qhs, const int* __restrict
   const int row0 = mp * TC_M;                                // this warp's rows: row0 .. row0 + 31
 
   int buf = 0;
-  for (int j0 = j_first; j0 <= p_max; j0 += TC_N) {
+  for (int j0 = j_start; j0 <= p_max; j0 = next_block(j0)) {
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();                                         // this block's tiles have landed; the block before is done with
-    const bool more = j0 + TC_N <= p_max;
-    if (nbuf == 2 && more) load_tiles(j0 + TC_N, buf ^ 1);
+    const int j_next = next_block(j0);
+    const bool more = j_next <= p_max;
+    if (nbuf == 2 && more) load_tiles(j_next, buf ^ 1);
     const __nv_bfloat16* sK = sK0 + buf * TC_N * ldk;
     const __nv_bfloat16* sV = sV0 + buf * TC_N * ldv;
     // ---- S = Q K^T for keys 8 w8 .. 8 w8 + 7 and this half's rows
@@ -214,7 +235,9 @@ attention_wide_tc_kernel(const float* q, int ldq, int qhs, const int* __restrict
 #pragma unroll
         for (int x = 0; x < 4; ++x) {
           const int r = row0 + m * 16 + g + (x >> 1) * 8, jj = w8 * 8 + tq4 * 2 + (x & 1);
-          sS[r * (TC_N + TC_SPAD) + jj] = s[m][x] * scale;
+          float sc = s[m][x] * scale;
+          if (softcap > 0.f) sc = softcap * tanhf(sc / softcap);
+          sS[r * (TC_N + TC_SPAD) + jj] = sc;
         }
     }
     __syncthreads();
@@ -225,7 +248,7 @@ attention_wide_tc_kernel(const float* q, int ldq, int qhs, const int* __restrict
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const int jj = my_sub * 8 + i, j = j0 + jj;
-        sv[i] = (j <= my_p && j >= my_lo) ? sS[my_row * (TC_N + TC_SPAD) + jj] : -INFINITY;
+        sv[i] = (j <= my_p && (j >= my_lo || j < keep_first)) ? sS[my_row * (TC_N + TC_SPAD) + jj] : -INFINITY;
         mb = fmaxf(mb, sv[i]);
       }
       mb = fmaxf(mb, __shfl_xor_sync(0xffffffffu, mb, 1));
@@ -285,7 +308,7 @@ attention_wide_tc_kernel(const float* q, int ldq, int qhs, const int* __restrict
       buf ^= 1;
     } else if (more) {
       __syncthreads();                                       // one buffer: everybody is done with it before it is refilled
-      load_tiles(j0 + TC_N, 0);
+      load_tiles(j_next, 0);
     }
   }
   if (my_sub == 0) sL[my_row] = l_run;
@@ -327,12 +350,17 @@ attention_wide_tc_kernel(const float* q, int ldq, int qhs, const int* __restrict
         const int tq = r / HG, h = h0 + r % HG;
         if (tq >= nq) continue;
         const float l = sL[r];
-        float f = l > 0.f ? 1.f / l : 0.f;
-        const int t = t0 + tq;
-        if (gate) f *= 1.f / (1.f + expf(-__bfloat162float(gate[(size_t)t * ldg + h])));
-        TO* op = out + (size_t)t * ldo + (size_t)h * ohs + nt * 8 + tq4 * 2;
-        op[0] = from_f<TO>(o[i][m][half * 2] * f);
-        op[1] = from_f<TO>(o[i][m][half * 2 + 1] * f);
+        const float f = l > 0.f ? 1.f / l : 0.f;
+        const int t = t0 + tq, col = nt * 8 + tq4 * 2;
+        float g0 = 1.f, g1 = 1.f;
+        if (gate) {
+          const __nv_bfloat16* gp = gate + (size_t)t * ldg + (gate_cols ? (size_t)h * Dv + col : (size_t)h);
+          g0 = 1.f / (1.f + expf(-__bfloat162float(gp[0])));
+          g1 = gate_cols ? 1.f / (1.f + expf(-__bfloat162float(gp[1]))) : g0;
+        }
+        TO* op = out + (size_t)t * ldo + (size_t)h * ohs + col;
+        op[0] = from_f<TO>(o[i][m][half * 2] * f * g0);
+        op[1] = from_f<TO>(o[i][m][half * 2 + 1] * f * g1);
       }
   }
 }
@@ -341,14 +369,15 @@ attention_wide_tc_kernel(const float* q, int ldq, int qhs, const int* __restrict
 template <typename TO>
 __global__ void attention_wide_merge_kernel(const int* __restrict__ tiles, int Hq, int Dv, int window, int chunk, int bps,
                                             int n_rel, const float* scratch, const __nv_bfloat16* gate, int ldg,
-                                            TO* __restrict__ out, int ldo, int ohs) {
+                                            TO* __restrict__ out, int ldo, int ohs, int keep_first, int gate_cols) {
   const int tile = blockIdx.x, h = blockIdx.y;
   if (tiles[4 * tile + 1] <= 0) return;
   const int t = tiles[4 * tile], p = tiles[4 * tile + 3];
   int lo = 0;
   if (window > 0 && p - window + 1 > lo) lo = p - window + 1;
   if (chunk > 0 && (p / chunk) * chunk > lo) lo = (p / chunk) * chunk;
-  const int nz = (p / TC_N) / bps - (lo / TC_N) / bps + 1;
+  const int kept_end = min((min(keep_first, lo) + TC_N - 1) / TC_N * TC_N, (lo / TC_N) * TC_N);
+  const int nz = (kept_end / TC_N + bps - 1) / bps + (p / TC_N) / bps - (lo / TC_N) / bps + 1;
   pdl_wait();
   pdl_trigger();
   scratch = after_wait(scratch);
@@ -362,37 +391,43 @@ __global__ void attention_wide_merge_kernel(const int* __restrict__ tiles, int H
     const float mz = sp[z * stride + Dv];
     if (mz != -INFINITY) L = fmaf(expf(mz - M), sp[z * stride + Dv + 1], L);
   }
-  float f = L > 0.f ? 1.f / L : 0.f;
-  if (gate) f *= 1.f / (1.f + expf(-__bfloat162float(gate[(size_t)t * ldg + h])));
+  const float f = L > 0.f ? 1.f / L : 0.f;
   for (int c = threadIdx.x; c < Dv; c += blockDim.x) {
     float a = 0.f;
     for (int z = 0; z < nz; ++z) {
       const float mz = sp[z * stride + Dv];
       if (mz != -INFINITY) a = fmaf(expf(mz - M), sp[z * stride + c], a);
     }
-    out[(size_t)t * ldo + (size_t)h * ohs + c] = from_f<TO>(a * f);
+    float gt = 1.f;
+    if (gate) gt = 1.f / (1.f + expf(-__bfloat162float(gate[(size_t)t * ldg + (gate_cols ? (size_t)h * Dv + c : (size_t)h)])));
+    out[(size_t)t * ldo + (size_t)h * ohs + c] = from_f<TO>(a * f * gt);
   }
 }
 
 constexpr int TC_BPS = 1;     // key blocks a CTA of a split single row takes: a constant, never a function of the batch
 
 // Blocks of keys a single row can touch: the positions it can see, in blocks, and one more for a ragged start.
-static int tc_blocks(int window, int chunk, int max_len) {
+static int tc_blocks(int window, int chunk, int max_len, int keep_first = 0) {
   int span = max_len > 0 ? max_len : 1;
   if (window > 0 && window < span) span = window;
   if (chunk > 0 && chunk < span) span = chunk;
-  return (span + TC_N - 1) / TC_N + 1;
+  int kept = 0;
+  if (keep_first > 0 && window > 0) kept = (keep_first + TC_N - 1) / TC_N;
+  return (span + TC_N - 1) / TC_N + 1 + kept;
 }
 // Rows that see at most three blocks are not split; the others have room for this many partial results.
-static bool tc_splits_rows(int window, int chunk, int max_len) { return tc_blocks(window, chunk, max_len) > 3; }
-static int tc_splits(int window, int chunk, int max_len) {
-  return (tc_blocks(window, chunk, max_len) + TC_BPS - 1) / TC_BPS + 1;
+static bool tc_splits_rows(int window, int chunk, int max_len, int keep_first = 0) {
+  return tc_blocks(window, chunk, max_len, keep_first) > 3;
+}
+static int tc_splits(int window, int chunk, int max_len, int keep_first = 0) {
+  return (tc_blocks(window, chunk, max_len, keep_first) + TC_BPS - 1) / TC_BPS + 1;
 }
 
 // Floats of scratch memory that single rows need (0: rows that see few keys are not split).
-MLXB_EXPORT long long mlxb_attention_wide_tc_scratch(int n_rows, int Hq, int Dv, int window, int chunk, int max_len) {
-  if (!tc_splits_rows(window, chunk, max_len)) return 0;
-  return (long long)n_rows * Hq * tc_splits(window, chunk, max_len) * (Dv + 2);
+MLXB_EXPORT long long mlxb_attention_wide_tc_scratch(int n_rows, int Hq, int Dv, int window, int chunk, int max_len,
+                                                     int keep_first) {
+  if (!tc_splits_rows(window, chunk, max_len, keep_first)) return 0;
+  return (long long)n_rows * Hq * tc_splits(window, chunk, max_len, keep_first) * (Dv + 2);
 }
 
 // How a launch is laid out, or false if the sizes are not served (the caller then takes the kernel on the CUDA
@@ -449,7 +484,7 @@ MLXB_EXPORT int mlxb_attention_wide_tc(int out_f32, const float* q, int ldq, int
                                        int Hkv, int Dk, int Dv, int krs, int vrs, int window, int chunk, float scale,
                                        const float* talk, const void* k_pool, const void* v_pool, const void* gate,
                                        int ldg, void* out, int ldo, int ohs, int* status, float* scratch, int max_len,
-                                       cudaStream_t stream) {
+                                       float softcap, int keep_first, int gate_cols, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
   TcPlan pl;
   const int shared_v = v_pool == k_pool;
@@ -458,10 +493,11 @@ MLXB_EXPORT int mlxb_attention_wide_tc(int out_f32, const float* q, int ldq, int
     return mlxb_fail(MLXB_BAD_ARG, "attention (wide, tensor cores): %d/%d heads, sizes %d/%d in rows of %d/%d", Hq, Hkv,
                      Dk, Dv, krs, vrs);
   // single rows with scratch memory: their keys split over grid.z, then merged
-  const int n_rel = tc_splits(window, chunk, max_len);
+  if (window <= 0) keep_first = 0;           // without a window every earlier position is visible anyway
+  const int n_rel = tc_splits(window, chunk, max_len, keep_first);
   // (only while the rows alone leave SMs idle: with more CTAs than SMs a split adds work and nothing else; a row's
   // result is the same up to the rounding of the merge either way)
-  const bool split = tile_q == 1 && scratch != nullptr && tc_splits_rows(window, chunk, max_len) && (long long)n_tiles * (Hq / pl.HG) < mlxb_sm_count();
+  const bool split = tile_q == 1 && scratch != nullptr && tc_splits_rows(window, chunk, max_len, keep_first) && (long long)n_tiles * (Hq / pl.HG) < mlxb_sm_count();
   const int TQ = split ? 1 : TC_M * pl.MP / pl.HG;
   const int subs = (tile_q + TQ - 1) / TQ;
   const int bps = split ? TC_BPS : 0;
@@ -479,12 +515,12 @@ MLXB_EXPORT int mlxb_attention_wide_tc(int out_f32, const float* q, int ldq, int
     launch_pdl(kern, grid, block, (size_t)smem, stream, q, ldq, qhs, tiles, subs, TQ, pl.HG, block_table, max_pages,   \
                n_pages, page, Hq, Hkv, Dk, Dv, pl.DkE, pl.seg, pl.n_seg, krs, vrs, shared_v, window, chunk, scale, talk, \
                (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, (const __nv_bfloat16*)gate, ldg, (TO*)out,  \
-               ldo, ohs, status, bps, n_rel, scratch, pl.nbuf);                                                        \
+               ldo, ohs, status, bps, n_rel, scratch, pl.nbuf, softcap, keep_first, gate_cols);                        \
     if (split) {                                                                                                       \
       if (int e = mlxb_check_launch("attention (wide, tensor cores)")) return e;                                       \
       launch_pdl(attention_wide_merge_kernel<TO>, dim3(n_tiles, Hq), dim3(Dv >= 128 ? 128 : 64), 0, stream, tiles, Hq, \
                  Dv, window, chunk, bps, n_rel, (const float*)scratch, (const __nv_bfloat16*)gate, ldg, (TO*)out, ldo, \
-                 ohs);                                                                                                 \
+                 ohs, keep_first, gate_cols);                                                                          \
     }                                                                                                                  \
   } while (0)
   if (pl.MP == 2) {

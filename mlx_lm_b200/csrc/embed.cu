@@ -2,6 +2,8 @@
 //   h[t, :] = round(float(wte[tok[t], :]) + float(wpe[pos[t], :]))
 // The sum is formed in 32-bit and rounded once.  `wpe` may be null (a model
 // without a position table): then it is a plain gather.
+// Instead of a table the positions may add a sinusoid: column 2i gets sin(p * freq[i]), column 2i+1 the cosine
+// of the same angle (`freq` float32 [ceil(D/2)], the angle a float32 product, sincosf).
 // Ids outside the tables set a status bit and produce zeros instead of
 // reading out of bounds.
 #include "common.cuh"
@@ -12,12 +14,12 @@ template <typename T, typename TO = T>
 __global__ void embed_pos_kernel(const int* __restrict__ tok, const int* __restrict__ pos,
                                  const T* __restrict__ wte, const T* __restrict__ wpe,
                                  TO* __restrict__ out, int D, int V, int P, float scale,
-                                 int* __restrict__ status) {
+                                 int* __restrict__ status, const float* __restrict__ freq) {
   pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x;
   const int id = tok[t];
-  const int p = wpe ? pos[t] : 0;
+  const int p = (wpe || freq) ? pos[t] : 0;
   bool ok = true;
   if (id < 0 || id >= V) { ok = false; if (threadIdx.x == 0) atomicOr(status, MLXB_ST_TOKEN_RANGE); }
   if (wpe && (p < 0 || p >= P)) { ok = false; if (threadIdx.x == 0) atomicOr(status, MLXB_ST_POSITION_RANGE); }
@@ -31,6 +33,11 @@ __global__ void embed_pos_kernel(const int* __restrict__ tok, const int* __restr
   for (int d = threadIdx.x; d < D; d += blockDim.x) {
     float v = to_f(e[d]) * scale;
     if (q) v += to_f(q[d]);
+    if (freq) {
+      float sn, cs;
+      sincosf((float)p * freq[d >> 1], &sn, &cs);
+      v += (d & 1) ? cs : sn;
+    }
     o[d] = from_f<TO>(v);
   }
 }
@@ -39,21 +46,21 @@ __global__ void embed_pos_kernel(const int* __restrict__ tok, const int* __restr
 // whose residual stream is float32 whatever its weights are).
 MLXB_EXPORT int mlxb_embed_pos(int dtype, const int* tok, const int* pos, const void* wte, const void* wpe,
                                void* out, int T_, int D, int V, int P, float scale, int* status,
-                               int out_f32, cudaStream_t stream) {
+                               int out_f32, const float* freq, cudaStream_t stream) {
   if (T_ <= 0) return 0;
   if (D <= 0 || V <= 0) return mlxb_fail(MLXB_BAD_ARG, "embed_pos: width %d, vocabulary %d", D, V);
   const int threads = D >= 1024 ? 256 : (D >= 256 ? 128 : 64);
   if (dtype == MLXB_BF16 && out_f32)
     embed_pos_kernel<__nv_bfloat16, float><<<T_, threads, 0, stream>>>(tok, pos, (const __nv_bfloat16*)wte,
                                                                        (const __nv_bfloat16*)wpe, (float*)out, D, V, P,
-                                                                       scale, status);
+                                                                       scale, status, freq);
   else if (dtype == MLXB_F32)
     embed_pos_kernel<float><<<T_, threads, 0, stream>>>(tok, pos, (const float*)wte, (const float*)wpe,
-                                                        (float*)out, D, V, P, scale, status);
+                                                        (float*)out, D, V, P, scale, status, freq);
   else if (dtype == MLXB_BF16)
     embed_pos_kernel<__nv_bfloat16><<<T_, threads, 0, stream>>>(tok, pos, (const __nv_bfloat16*)wte,
                                                                 (const __nv_bfloat16*)wpe, (__nv_bfloat16*)out,
-                                                                D, V, P, scale, status);
+                                                                D, V, P, scale, status, freq);
   else
     return mlxb_fail(MLXB_BAD_DTYPE, "embed_pos: dtype code %d", dtype);
   return mlxb_check_launch("embed_pos");

@@ -180,12 +180,14 @@ def _call(libname: str, fname: str, argtypes, *args) -> None:
 # embedding + position add
 
 _EMBED_ARGS = [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float,
-               c_void_p, c_int, c_void_p]
+               c_void_p, c_int, c_void_p, c_void_p]
 
 
-def embed_pos(tokens, positions, wte, wpe, out, status, stream, scale: float = 1.0) -> None:
+def embed_pos(tokens, positions, wte, wpe, out, status, stream, scale: float = 1.0, freq=None) -> None:
     """``out[t] = wte[tokens[t]] * scale + wpe[positions[t]]`` (``wpe`` may be None).  ``out`` has the tables'
-    dtype, or is float32 over bfloat16 tables (a residual stream kept in float32)."""
+    dtype, or is float32 over bfloat16 tables (a residual stream kept in float32).  ``freq`` (float32
+    ``[ceil(width / 2)]``): a sinusoid of the position is added, column ``2i`` gets ``sin(p * freq[i])`` and
+    column ``2i + 1`` the cosine of the same angle."""
     _need(tokens, torch.int32, "embed_pos tokens")
     out_f32 = int(out.dtype == torch.float32 and wte.dtype == torch.bfloat16)
     if not out_f32:
@@ -198,8 +200,14 @@ def embed_pos(tokens, positions, wte, wpe, out, status, stream, scale: float = 1
         _need(wpe, wte.dtype, "embed_pos wpe")
         if wpe.shape[1] != D or not wpe.is_contiguous():
             raise KernelError(f"embed_pos: position table {tuple(wpe.shape)} against width {D}")
+    if freq is not None:
+        _need(positions, torch.int32, "embed_pos positions")
+        _need(freq, torch.float32, "embed_pos freq")
+        if freq.numel() != (D + 1) // 2 or not freq.is_contiguous():
+            raise KernelError(f"embed_pos: {freq.numel()} frequencies for width {D}")
     _call("embed", "mlxb_embed_pos", _EMBED_ARGS, dtype_code(wte.dtype), _p(tokens), _p(positions), _p(wte),
-          _p(wpe), _p(out), T, D, wte.shape[0], 0 if wpe is None else wpe.shape[0], scale, _p(status), out_f32, stream)
+          _p(wpe), _p(out), T, D, wte.shape[0], 0 if wpe is None else wpe.shape[0], scale, _p(status), out_f32,
+          _p(freq), stream)
 
 
 def gather_tokens(src, index, dst, status, stream) -> None:
@@ -906,18 +914,32 @@ def qkv_prepare(proj, q_off: int, k_off: int, v_off: int, n_heads: int, n_kv_hea
 
 _WIDE_ARGS = [c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
               c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
-              c_int, c_void_p, c_int, c_void_p, c_void_p]
+              c_int, c_void_p, c_int, c_void_p, c_float, c_int, c_int, c_void_p]
+
+
+def _wide_gate(gate, dtype, n_heads: int, value_dim: int, what: str):
+    """``(row stride, one gate per output column?)`` of a gate ``[T, n_heads]`` or ``[T, n_heads * value_dim]``."""
+    if gate is None:
+        return 0, 0
+    _need(gate, dtype, what + " gate")
+    if gate.shape[1] == n_heads * value_dim and value_dim > 1:
+        return _rows(gate, what + " gate"), 1
+    if gate.shape[1] != n_heads:
+        raise KernelError(f"{what}: gate {tuple(gate.shape)} for {n_heads} heads of {value_dim} columns")
+    return _rows(gate, what + " gate"), 0
 
 
 def attention_wide(q, q_head_stride: int, positions, token_req, block_table, k_pool, v_pool, out, out_head_stride: int,
                    n_heads: int, key_dim: int, value_dim: int, scale: float, status, stream, window: int = 0,
-                   chunk: int = 0, talk=None, gate=None, rows=None) -> None:
+                   chunk: int = 0, talk=None, gate=None, rows=None, softcap: float = 0.0, keep_first: int = 0) -> None:
     """Causal attention of float32 queries ``q [T, .]`` (head ``h`` from column ``h * q_head_stride``, ``key_dim``
     values) over pages ``k_pool [n_pages, kv_heads, page, key row]`` and ``v_pool [n_pages, kv_heads, page, value
     row]`` (``v_pool`` may be ``k_pool``: a value is then the first ``value_dim`` columns of the key row).  Position
     ``p`` sees ``j <= p`` with ``p - j < window`` (if ``window``) and ``j // chunk == p // chunk`` (if ``chunk``).
     ``talk``: float32 ``[n_heads, n_heads]``, the heads' scores mixed before the softmax; ``gate``: ``[T, n_heads]``
-    in the pools' dtype, head ``h``'s output times ``sigmoid(gate[t, h])``.  ``out``: the pools' dtype or float32."""
+    in the pools' dtype, head ``h``'s output times ``sigmoid(gate[t, h])``, or ``[T, n_heads * value_dim]``, a gate per
+    output column.  ``softcap``: scores become ``softcap * tanh(s / softcap)`` before the softmax (0: as they are).
+    ``keep_first``: beside the window, positions ``j < keep_first`` stay visible.  ``out``: the pools' dtype or float32."""
     _need(q, torch.float32, "attention_wide q")
     _need(k_pool, None, "attention_wide k_pool")
     _need(v_pool, k_pool.dtype, "attention_wide v_pool")
@@ -931,23 +953,19 @@ def attention_wide(q, q_head_stride: int, positions, token_req, block_table, k_p
         _need(talk, torch.float32, "attention_wide talk")
         if talk.shape != (n_heads, n_heads) or not talk.is_contiguous():
             raise KernelError(f"attention_wide: talk {tuple(talk.shape)} for {n_heads} heads")
-    ldg = 0
-    if gate is not None:
-        _need(gate, k_pool.dtype, "attention_wide gate")
-        if gate.shape[1] != n_heads:
-            raise KernelError(f"attention_wide: gate {tuple(gate.shape)} for {n_heads} heads")
-        ldg = _rows(gate, "attention_wide gate")
+    ldg, gate_cols = _wide_gate(gate, k_pool.dtype, n_heads, value_dim, "attention_wide")
     n = q.shape[0] if rows is None else rows.numel()
     _call("attention_wide", "mlxb_attention_wide", _WIDE_ARGS, dtype_code(k_pool.dtype), int(out.dtype == torch.float32
           and k_pool.dtype != torch.float32), _p(q), _rows(q, "attention_wide q"), q_head_stride, _p(positions),
           _p(token_req), _p(block_table), block_table.shape[1], n_pages, page, n_heads, Hkv, key_dim, value_dim, krs, vrs,
           int(window or 0), int(chunk or 0), float(scale), _p(talk), _p(k_pool), _p(v_pool), _p(gate), ldg, _p(out),
-          _rows(out, "attention_wide out"), out_head_stride, _p(rows), n, _p(status), stream)
+          _rows(out, "attention_wide out"), out_head_stride, _p(rows), n, _p(status), float(softcap or 0.0),
+          int(keep_first or 0) if window else 0, gate_cols, stream)
 
 
 _WIDE_TC_ARGS = [c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                  c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
-                 c_int, c_void_p, c_void_p, c_int, c_void_p]
+                 c_int, c_void_p, c_void_p, c_int, c_float, c_int, c_int, c_void_p]
 
 WIDE_TC = _os.environ.get("MLXB_WIDE_TC", "1") != "0"     # 0: the kernel on the CUDA cores for bfloat16 too
 
@@ -962,17 +980,19 @@ def attention_wide_tc_supported(k_pool, v_pool, n_heads: int, key_dim: int, valu
                   int(v_pool.data_ptr() == k_pool.data_ptr())))
 
 
-def attention_wide_scratch(n_rows: int, n_heads: int, value_dim: int, window: int, chunk: int, max_len: int) -> int:
+def attention_wide_scratch(n_rows: int, n_heads: int, value_dim: int, window: int, chunk: int, max_len: int,
+                           keep_first: int = 0) -> int:
     """Floats of scratch memory with which ``attention_wide_tiles`` splits the keys of single rows over several
     CTAs (0: rows that see few keys are not split)."""
-    f, _ = _fn("attention_wide_tc", "mlxb_attention_wide_tc_scratch", [c_int] * 6)
+    f, _ = _fn("attention_wide_tc", "mlxb_attention_wide_tc_scratch", [c_int] * 7)
     f.restype = ctypes.c_longlong
-    return int(f(n_rows, n_heads, value_dim, int(window or 0), int(chunk or 0), max_len))
+    return int(f(n_rows, n_heads, value_dim, int(window or 0), int(chunk or 0), max_len, int(keep_first or 0)))
 
 
 def attention_wide_tiles(q, q_head_stride: int, tiles, n_tiles: int, tile_queries: int, block_table, k_pool, v_pool, out,
                          out_head_stride: int, n_heads: int, key_dim: int, value_dim: int, scale: float, status, stream,
-                         window: int = 0, chunk: int = 0, talk=None, gate=None, scratch=None, max_len: int = 0) -> None:
+                         window: int = 0, chunk: int = 0, talk=None, gate=None, scratch=None, max_len: int = 0,
+                         softcap: float = 0.0, keep_first: int = 0) -> None:
     """``attention_wide`` on tensor cores for bfloat16 pools.  Instead of token rows it takes tiles, int32
     ``[n_tiles, 4]`` = (first token row, queries, block-table row, first position) of at most ``tile_queries``
     consecutive tokens of one request each (tiles of 0 queries are skipped).  With ``scratch`` (float32, at least
@@ -991,39 +1011,37 @@ def attention_wide_tiles(q, q_head_stride: int, tiles, n_tiles: int, tile_querie
         _need(talk, torch.float32, "attention_wide_tiles talk")
         if talk.shape != (n_heads, n_heads) or not talk.is_contiguous():
             raise KernelError(f"attention_wide_tiles: talk {tuple(talk.shape)} for {n_heads} heads")
-    ldg = 0
-    if gate is not None:
-        _need(gate, torch.bfloat16, "attention_wide_tiles gate")
-        if gate.shape[1] != n_heads:
-            raise KernelError(f"attention_wide_tiles: gate {tuple(gate.shape)} for {n_heads} heads")
-        ldg = _rows(gate, "attention_wide_tiles gate")
+    ldg, gate_cols = _wide_gate(gate, torch.bfloat16, n_heads, value_dim, "attention_wide_tiles")
     _call("attention_wide_tc", "mlxb_attention_wide_tc", _WIDE_TC_ARGS, int(out.dtype == torch.float32), _p(q),
           _rows(q, "attention_wide_tiles q"), q_head_stride, _p(tiles), n_tiles, tile_queries, _p(block_table),
           block_table.shape[1], n_pages, page, n_heads, Hkv, key_dim, value_dim, krs, v_pool.shape[3], int(window or 0),
           int(chunk or 0), float(scale), _p(talk), _p(k_pool), _p(v_pool), _p(gate), ldg, _p(out),
-          _rows(out, "attention_wide_tiles out"), out_head_stride, _p(status), _p(scratch), int(max_len), stream)
+          _rows(out, "attention_wide_tiles out"), out_head_stride, _p(status), _p(scratch), int(max_len),
+          float(softcap or 0.0), int(keep_first or 0), gate_cols, stream)
 
 
 def attention_wide_step(ctx, q, q_head_stride: int, cache_k, cache_v, block_table, out, out_head_stride: int, n_heads: int,
                         key_dim: int, value_dim: int, scale: float, window: int = 0, chunk: int = 0, talk=None,
-                        gate=None) -> None:
+                        gate=None, softcap: float = 0.0, keep_first: int = 0) -> None:
     """All of a step's rows through ``attention_wide``: on tensor cores where the sizes allow it (the portions' tiles
     and the single-token rows are two launches), else on the CUDA cores (float32 runs, odd sizes)."""
     if attention_wide_tc_supported(cache_k, cache_v, n_heads, key_dim, value_dim, talk is not None):
         if ctx.n_portion and ctx.portion_tiles is not None:
             attention_wide_tiles(q, q_head_stride, ctx.portion_tiles, ctx.n_portion_tiles, PREFILL_TILE, block_table,
                                  cache_k, cache_v, out, out_head_stride, n_heads, key_dim, value_dim, scale, ctx.status,
-                                 ctx.stream, window=window, chunk=chunk, talk=talk, gate=gate)
+                                 ctx.stream, window=window, chunk=chunk, talk=talk, gate=gate, softcap=softcap,
+                                 keep_first=keep_first)
         if ctx.n_single and ctx.single_tiles is not None:
-            need = attention_wide_scratch(ctx.n_single, n_heads, value_dim, window, chunk, ctx.max_len)
+            need = attention_wide_scratch(ctx.n_single, n_heads, value_dim, window, chunk, ctx.max_len, keep_first)
             scratch = ctx.ws.flat("attn_wide_partial", need, torch.float32) if need else None
             attention_wide_tiles(q, q_head_stride, ctx.single_tiles, ctx.n_single, 1, block_table, cache_k, cache_v, out,
                                  out_head_stride, n_heads, key_dim, value_dim, scale, ctx.status, ctx.stream,
-                                 window=window, chunk=chunk, talk=talk, gate=gate, scratch=scratch, max_len=ctx.max_len)
+                                 window=window, chunk=chunk, talk=talk, gate=gate, scratch=scratch, max_len=ctx.max_len,
+                                 softcap=softcap, keep_first=keep_first)
         return
     attention_wide(q, q_head_stride, ctx.positions, ctx.token_req, block_table, cache_k, cache_v, out, out_head_stride,
                    n_heads, key_dim, value_dim, scale, ctx.status, ctx.stream, window=window, chunk=chunk, talk=talk,
-                   gate=gate)
+                   gate=gate, softcap=softcap, keep_first=keep_first)
 
 
 # --------------------------------------------------------------------------
@@ -1128,6 +1146,120 @@ def wkv_scan(rkv, r_off: int, k_off: int, v_off: int, decay_raw, bonus, state, s
     _call("wkv", "mlxb_wkv_scan", _WKV_ARGS, dtype_code(rkv.dtype), _p(rkv), _rows(rkv, "wkv_scan rkv"), r_off, k_off,
           v_off, _p(decay_raw), _rows(decay_raw, "wkv_scan decay"), _p(bonus), _p(state), _p(slots), _p(token_req),
           _p(req_first_token), _p(o), _rows(o, "wkv_scan o"), H, K, V, slots.numel(), stream)
+
+
+# --------------------------------------------------------------------------
+# Dynamic Tanh norm and the stream update through it (csrc/dyt.cu)
+
+def dyt_norm(x, alpha, weight, bias, out, stream, rows=None, out_scale: float = 1.0) -> None:
+    """``out[r] = (tanh(alpha * x[rows[r]]) * weight + bias) * out_scale`` over float32 rows; ``alpha``: one float32
+    number on the device; ``out`` in the activation dtype or float32."""
+    _need(x, torch.float32, "dyt_norm x")
+    for t, what in ((alpha, "alpha"), (weight, "weight")) + (((bias, "bias"),) if bias is not None else ()):
+        _need(t, torch.float32, "dyt_norm " + what)
+    D = x.shape[1]
+    R = x.shape[0] if rows is None else rows.numel()
+    if out.shape != (R, D) or weight.numel() != D or alpha.numel() != 1 or (bias is not None and bias.numel() != D):
+        raise KernelError(f"dyt_norm: x {tuple(x.shape)}, out {tuple(out.shape)}, weight {tuple(weight.shape)}")
+    _call("dyt", "mlxb_dyt_norm", [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_float,
+                                   c_void_p, c_int, c_int, c_int, c_void_p],
+          dtype_code(out.dtype), _p(x), _rows(x, "dyt_norm x"), _p(rows), x.shape[0], _p(alpha), _p(weight), _p(bias),
+          float(out_scale), _p(out), _rows(out, "dyt_norm out"), R, D, stream)
+
+
+def dyt_residual(x, branch, stream, post=None, nxt=None, next_out=None, terms: int = 1, token_req=None) -> None:
+    """``x[t] += f(sum_k branch[t * terms + k])`` over float32 rows, with ``f = tanh(alpha * .) * weight + bias`` for
+    ``post = (alpha, weight, bias)`` (None: the identity); then, with ``nxt = (alpha, weight, bias)`` and ``next_out``
+    (activation dtype or float32 ``[T, D]``), the same kind of norm of the new rows is left in ``next_out``.  Rows
+    whose ``token_req`` is negative are skipped."""
+    _need(x, torch.float32, "dyt_residual x")
+    _need(branch, torch.float32, "dyt_residual branch")
+    T, D = x.shape
+    if branch.shape != (T * terms, D):
+        raise KernelError(f"dyt_residual: branch {tuple(branch.shape)} for {T} rows of {terms} term(s)")
+    pa = pw = pb = na = nw = nb = None
+    if post is not None:
+        pa, pw, pb = post
+    if nxt is not None:
+        na, nw, nb = nxt
+        if next_out is None or next_out.shape != (T, D):
+            raise KernelError("dyt_residual: the next norm needs an output of the stream's shape")
+    for t in (pa, pw, pb, na, nw, nb):
+        if t is not None:
+            _need(t, torch.float32, "dyt_residual norm tensor")
+    _call("dyt", "mlxb_dyt_residual", [c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                       c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+          dtype_code(next_out.dtype) if nxt is not None else F32, _p(x), _rows(x, "dyt_residual x"), _p(branch),
+          _rows(branch, "dyt_residual branch"), int(terms), _p(token_req), _p(pa), _p(pw), _p(pb), _p(na), _p(nw), _p(nb),
+          _p(next_out) if nxt is not None else None, _rows(next_out, "dyt_residual next") if nxt is not None else 0,
+          T, D, stream)
+
+
+# --------------------------------------------------------------------------
+# a feed-forward of many small experts (csrc/moe.cu)
+
+MOE_SCORES = {"sigmoid": 0, "softmax": 1}
+
+
+def moe_tile_rows(tensor_cores: bool) -> int:
+    """Slots a tile of the experts' products takes: of the tensor-core kernel, or of the one on the CUDA cores."""
+    f, _ = _fn("moe", "mlxb_moe_tile_rows", [c_int])
+    return int(f(int(bool(tensor_cores))))
+
+
+def moe_route(logits, token_req, top: int, sel_expert, sel_weight, stream, score: str = "sigmoid",
+              renormalize: bool = False) -> None:
+    """Per token the ``top`` experts with the largest scores (``sigmoid`` of the float32 router logits ``[T, E]``, or
+    their ``softmax``) into ``sel_expert`` int32 ``[T * top]`` and their scores into ``sel_weight`` float32
+    ``[T * top]`` (``renormalize``: divided by their sum).  Rows whose ``token_req`` is negative get expert -1."""
+    _need(logits, torch.float32, "moe_route logits")
+    _need(sel_expert, torch.int32, "moe_route sel_expert")
+    _need(sel_weight, torch.float32, "moe_route sel_weight")
+    T, E = logits.shape
+    if sel_expert.numel() < T * top or sel_weight.numel() < T * top or score not in MOE_SCORES:
+        raise KernelError(f"moe_route: {T} tokens, {top} of {E} experts, score {score!r}")
+    _call("moe", "mlxb_moe_route", [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                                    c_void_p],
+          _p(logits), _rows(logits, "moe_route logits"), _p(token_req), T, E, int(top), MOE_SCORES[score],
+          int(bool(renormalize)), _p(sel_expert), _p(sel_weight), stream)
+
+
+def moe_max_tiles(n_slots: int, n_experts: int, tile_rows: int) -> int:
+    """The most tiles ``n_slots`` (token, choice) pairs can make, however they fall on the experts."""
+    return (n_slots + tile_rows - 1) // tile_rows + n_experts
+
+
+def moe_plan(sel_expert, n_slots: int, n_experts: int, tile_rows: int, sorted_slots, tile_info, n_tiles, stream) -> None:
+    """The slots sorted by expert (``sorted_slots`` int32 ``[n_slots]``) and the tiles of at most ``tile_rows`` slots
+    of one expert (``tile_info`` int32 ``[moe_max_tiles, 3]`` = expert, first place, slots; ``n_tiles`` int32 ``[1]``)."""
+    for t, what in ((sel_expert, "sel_expert"), (sorted_slots, "sorted"), (tile_info, "tile_info"), (n_tiles, "n_tiles")):
+        _need(t, torch.int32, "moe_plan " + what)
+    max_tiles = moe_max_tiles(n_slots, n_experts, tile_rows)
+    if sorted_slots.numel() < n_slots or tile_info.numel() < 3 * max_tiles or sel_expert.numel() < n_slots:
+        raise KernelError(f"moe_plan: {n_slots} slots, {n_experts} experts")
+    _call("moe", "mlxb_moe_plan", [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+          _p(sel_expert), n_slots, n_experts, tile_rows, max_tiles, _p(sorted_slots), _p(tile_info), _p(n_tiles), stream)
+
+
+def moe_gemm(a, a_div: int, w, n_out: int, sorted_slots, tile_info, n_tiles, max_tiles: int, tile_rows: int, out, stream,
+             sel_weight=None, gated: bool = False) -> None:
+    """``out[slot] = a[slot // a_div] @ w[expert(slot)].T`` for every slot of the plan; ``w [E, n_out, K]``.  ``gated``:
+    ``w [E, 2 n_out, K]`` holds gate rows then up rows and the result is ``silu(s g) * (s u)`` with ``s`` the slot's
+    routing weight.  ``out``: ``a``'s dtype or float32, ``[n_slots, n_out]``."""
+    _need(a, None, "moe_gemm a")
+    _need(w, a.dtype, "moe_gemm w")
+    E, NW, K = w.shape
+    if NW != (2 if gated else 1) * n_out or a.shape[1] != K or out.shape[1] != n_out or not w.is_contiguous():
+        raise KernelError(f"moe_gemm: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    if out.dtype not in (a.dtype, torch.float32):
+        raise KernelError(f"moe_gemm: out {out.dtype} for inputs {a.dtype}")
+    if gated:
+        _need(sel_weight, torch.float32, "moe_gemm sel_weight")
+    _call("moe", "mlxb_moe_gemm", [c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p, ctypes.c_longlong, c_int, c_int,
+                                   c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p],
+          dtype_code(a.dtype), int(out.dtype == torch.float32 and a.dtype != torch.float32), int(bool(gated)), _p(a),
+          _rows(a, "moe_gemm a"), int(a_div), _p(w), NW * K, n_out, K, _p(sorted_slots), _p(tile_info), _p(n_tiles),
+          int(max_tiles), int(tile_rows), _p(sel_weight), _p(out), _rows(out, "moe_gemm out"), stream)
 
 
 # --------------------------------------------------------------------------

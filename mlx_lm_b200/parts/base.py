@@ -8,7 +8,8 @@ Kinds of parts and the interface each must have
 ``Norm``            ``forward(ctx, x, rows=None) -> y``  (``rows``: int32
                     device tensor selecting input rows)
 ``PositionEncoding`` ``embedding_table()`` (table added to the token embedding
-                    by position, or None), ``rotate(ctx, q, k)`` (in place, on
+                    by position, or None), ``embedding_frequencies()`` (a sinusoid
+                    added there instead, or None), ``rotate(ctx, q, k)`` (in place, on
                     this step's queries and keys, before keys enter the cache)
                     and ``max_positions`` (None = unbounded)
 ``Mixer``           ``cache_spec()`` (what it keeps per request: a
@@ -55,12 +56,15 @@ class PagedKVSpec:
     """Keys and values of every position (``window=None``) or of the last ``window`` positions.  ``chunk``: a
     position reads only keys of its own run of ``chunk`` positions (runs counted from position 0), so pages that
     lie wholly before the current run are given back.  ``value_dim``: width of a value row if it differs from
-    ``head_dim``; 0: no value pool at all, values are read out of the key rows (a cache of latent rows)."""
+    ``head_dim``; 0: no value pool at all, values are read out of the key rows (a cache of latent rows).
+    ``keep_first``: beside a window, the first so many positions of the sequence stay readable for good (their pages
+    are never given back)."""
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     chunk: Optional[int] = None
     value_dim: Optional[int] = None
+    keep_first: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -145,6 +149,11 @@ class PositionEncoding(Part):
     max_positions: Optional[int] = None
 
     def embedding_table(self) -> Optional[torch.Tensor]:
+        return None
+
+    def embedding_frequencies(self) -> Optional[torch.Tensor]:
+        """float32 ``[ceil(width / 2)]``: a sinusoid added at the embedding (column ``2i``: the sine of
+        ``position * f[i]``, column ``2i + 1``: its cosine), or None."""
         return None
 
     def rotate(self, ctx, q, k) -> None:

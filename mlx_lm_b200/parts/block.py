@@ -10,6 +10,7 @@ from typing import Optional
 
 import torch
 
+from .. import ops
 from .base import Block, FeedForward, Mixer, Norm, register_part
 
 # In bfloat16 a block lets its mixer and its feed-forward fold the norm before them into their first linear
@@ -73,5 +74,74 @@ class StreamBlock(Block):
         return x
 
 
+class SandwichBlock(Block):
+    """A block over a float32 residual stream with a norm before AND after each sublayer:
+    ``x += post_1(mixer(norm_1(x)))``, then, if the layer has a feed-forward, ``x += post_2(feed_forward(norm_2(x)))``.
+
+    The sublayers leave their results in float32 (``mixer.mix(ctx, x, cache) -> [T, width]``,
+    ``feed_forward.branch(ctx, x) -> ([T * terms, width], terms)``: a feed-forward of experts hands over one row per
+    (token, chosen expert), summed in the update).  The post-norms are elementwise (``Norm.stream_args()``), so one
+    kernel does the sum over terms, the post-norm, the add to the stream and the norm that reads the stream next:
+    ``norm_2`` of this block, or ``norm_1`` of the block named by ``feeds`` (the one that runs next), whose input
+    then waits in ``ctx.carried``.  Norms in front that are not elementwise run as kernels of their own."""
+    replayable = True
+    kernel_libs = ("dyt",)
+
+    def __init__(self, norm_1: Norm, mixer: Mixer, post_1: Norm, norm_2: Optional[Norm] = None,
+                 feed_forward: Optional[FeedForward] = None, post_2: Optional[Norm] = None,
+                 feeds: Optional["SandwichBlock"] = None):
+        if not (norm_2 is None) == (feed_forward is None) == (post_2 is None):
+            raise ValueError("a feed-forward comes with the norm before it and the norm after it")
+        self.norm_1, self.mixer, self.post_1 = norm_1, mixer, post_1
+        self.norm_2, self.feed_forward, self.post_2 = norm_2, feed_forward, post_2
+        self.feeds = feeds
+
+    def children(self):
+        return tuple(p for p in (self.norm_1, self.mixer, self.post_1, self.norm_2, self.feed_forward, self.post_2)
+                     if p is not None)
+
+    def cache_spec(self):
+        return self.mixer.cache_spec()
+
+    @staticmethod
+    def _fusable(norm: Optional[Norm]) -> bool:
+        return norm is not None and hasattr(norm, "stream_args") and getattr(norm, "out_scale", 1.0) == 1.0
+
+    def _update(self, ctx, x, branch, terms: int, post: Norm, nxt: Optional[Norm], tag: str, name: str):
+        T, D = x.shape
+        out = None
+        if self._fusable(nxt):
+            out = ctx.ws.get(tag, T, D, ctx.dtype)
+        ops.label(name, (12.0 + terms) * T * D, (8.0 + 4.0 * terms + (out.element_size() if out is not None else 0)) * T * D)
+        ops.dyt_residual(x, branch, ctx.stream, post=post.stream_args(), nxt=nxt.stream_args() if out is not None else None,
+                         next_out=out, terms=terms, token_req=ctx.token_req)
+        return out
+
+    def forward(self, ctx, x, cache):
+        carried = getattr(ctx, "carried", None)
+        ctx.carried = None
+        if carried is not None and carried[0] is self.norm_1:
+            n1 = carried[1]
+        else:
+            n1 = self.norm_1.forward(ctx, x)
+        y = self.mixer.mix(ctx, n1, cache)
+        if self.feed_forward is None:
+            nxt = self.feeds.norm_1 if self.feeds is not None else None
+            out = self._update(ctx, x, y, 1, self.post_1, nxt, "normed", self.post_1.name)
+            if out is not None:
+                ctx.carried = (nxt, out)
+            return x
+        n2 = self._update(ctx, x, y, 1, self.post_1, self.norm_2, "normed_2", self.post_1.name)
+        if n2 is None:
+            n2 = self.norm_2.forward(ctx, x, tag="normed_2")
+        yb, terms = self.feed_forward.branch(ctx, n2)
+        nxt = self.feeds.norm_1 if self.feeds is not None else None
+        out = self._update(ctx, x, yb, terms, self.post_2, nxt, "normed", self.post_2.name)
+        if out is not None:
+            ctx.carried = (nxt, out)
+        return x
+
+
 register_part("block", "pre_norm", PreNormBlock)
+register_part("block", "sandwich", SandwichBlock)
 register_part("block", "stream", StreamBlock)

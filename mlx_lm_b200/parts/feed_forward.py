@@ -63,8 +63,104 @@ class GatedMLP(FeedForward):
         ops.gated_unit(both, h, ctx.stream)
         return self.down.forward(ctx, h, residual, residual=residual)
 
+    def branch(self, ctx, x):
+        """The result alone, float32 ``[T, width]``, for a block that adds it to the stream itself: ``(rows, 1)``."""
+        T = x.shape[0]
+        both = ctx.ws.get("ffn_gate_up", T, 2 * self.inner, x.dtype)
+        self.gate_up.forward(ctx, x, both)
+        h = ctx.ws.get("ffn_hidden", T, self.inner, x.dtype)
+        ops.label(self.name + ".act", 4.0 * T * self.inner, 3.0 * x.element_size() * T * self.inner)
+        ops.gated_unit(both, h, ctx.stream)
+        return self.down.forward(ctx, h, ctx.ws.get("ffn_out", T, self.width, torch.float32)), 1
+
 
 register_part("feed_forward", "gated_mlp", GatedMLP)
+
+
+class ExpertsMLP(FeedForward):
+    """A mixture of experts: ``n_experts`` small gated feed-forwards ``down(silu(gate(z)) * up(z))`` without biases
+    (``<name>.e<i>.gate|up|down``), of which every token uses the ``top`` with the largest router scores.
+
+    The router (``<name>.router`` ``[n_experts, width]``) gives float32 logits; ``score``: ``sigmoid`` of each, or the
+    ``softmax`` over the experts; the chosen experts' scores are the weights, divided by their sum only with
+    ``renormalize``.  ``scale_input``: the weight multiplies the expert's INPUT, ``sum_c expert_c(w_c x)``; else its
+    output, ``sum_c w_c expert_c(x)``.  (With the input scaled, ``w`` is applied to the float32 sums of the gate and up
+    products, which are linear in the input.)
+
+    The experts' weights are stacked at bind time (``[E, 2 inner, width]`` gate rows then up rows, ``[E, width,
+    inner]``); a step routes (``ops.moe_route``), sorts its (token, choice) slots by expert into tiles
+    (``ops.moe_plan``) and runs two products over the tiles (``ops.moe_gemm``), the gated unit in the first one's
+    epilogue.  ``branch`` returns one float32 row per slot, ``top`` rows a token, which the caller sums in the order
+    of the choices; ``forward`` adds them to a float32 stream."""
+    replayable = True
+    kernel_libs = ("moe", "dyt")
+
+    def __init__(self, name: str, width: int, inner: int, n_experts: int, top: int, score: str = "sigmoid",
+                 renormalize: bool = False, scale_input: bool = True, router_name: str = "router",
+                 expert_prefix: str = "e", gate_name: str = "gate", up_name: str = "up", down_name: str = "down",
+                 init: Init = Init(), router_init: Init = Init()):
+        if not 1 <= top <= n_experts:
+            raise ValueError(f"{name}: {top} of {n_experts} experts")
+        if score not in ops.MOE_SCORES:
+            raise ValueError(f"{name}: router score {score!r} is not one of {sorted(ops.MOE_SCORES)}")
+        if not scale_input:
+            raise ValueError(f"{name}: only routing weights on the experts' inputs are built")
+        self.name, self.width, self.inner, self.n_experts, self.top = name, width, inner, n_experts, top
+        self.score, self.renormalize, self.scale_input = score, renormalize, scale_input
+        self.router = Linear(f"{name}.{router_name}", width, n_experts, bias=False, weight_suffix="", init=router_init)
+        self.names = [(f"{name}.{expert_prefix}{e}.{gate_name}", f"{name}.{expert_prefix}{e}.{up_name}",
+                       f"{name}.{expert_prefix}{e}.{down_name}") for e in range(n_experts)]
+        self.init = init
+        self.w_in = self.w_out = None
+
+    def children(self):
+        return (self.router,)
+
+    def param_specs(self):
+        from .base import MATRIX
+        specs = []
+        for g, u, d in self.names:
+            specs += [ParamSpec(g, (self.inner, self.width), MATRIX, self.init),
+                      ParamSpec(u, (self.inner, self.width), MATRIX, self.init),
+                      ParamSpec(d, (self.width, self.inner), MATRIX, Init(0.0, self.inner ** -0.5))]
+        return specs
+
+    def bind(self, tensors, dtype, device) -> None:
+        self.w_in = torch.stack([torch.cat([tensors[g], tensors[u]], dim=0) for g, u, _ in self.names]).contiguous()
+        self.w_out = torch.stack([tensors[d] for _, _, d in self.names]).contiguous()
+
+    def branch(self, ctx, x):
+        T, E, top, F_, D = x.shape[0], self.n_experts, self.top, self.inner, self.width
+        S = T * top
+        logits = self.router.forward(ctx, x, ctx.ws.get("moe_logits", T, (E + 7) // 8 * 8, torch.float32)[:, :E])
+        sel_e = ctx.ws.flat("moe_sel_expert", S, torch.int32)
+        sel_w = ctx.ws.flat("moe_sel_weight", S, torch.float32)
+        ops.label(self.name + ".route", 8.0 * T * E, 4.0 * T * E + 8.0 * S)
+        ops.moe_route(logits, ctx.token_req, top, sel_e, sel_w, ctx.stream, score=self.score, renormalize=self.renormalize)
+        tc = x.dtype == torch.bfloat16 and D % 8 == 0 and F_ % 8 == 0 and x.stride(0) % 8 == 0
+        rows = ops.moe_tile_rows(tc)
+        max_tiles = ops.moe_max_tiles(S, E, rows)
+        order = ctx.ws.flat("moe_sorted", S, torch.int32)
+        tiles = ctx.ws.flat("moe_tiles", 3 * max_tiles + 1, torch.int32)
+        n_tiles = tiles[3 * max_tiles:]
+        ops.moe_plan(sel_e, S, E, rows, order, tiles, n_tiles, ctx.stream)
+        h = ctx.ws.get("moe_hidden", S, F_, x.dtype)
+        es = x.element_size()
+        ops.label(self.name + ".experts.in", 4.0 * S * D * F_, es * (min(E, S) * 2 * F_ * D + T * D + S * F_))
+        ops.moe_gemm(x, top, self.w_in, F_, order, tiles, n_tiles, max_tiles, rows, h, ctx.stream, sel_weight=sel_w, gated=True)
+        y = ctx.ws.get("moe_out", S, D, torch.float32)
+        ops.label(self.name + ".experts.out", 2.0 * S * D * F_, es * (min(E, S) * F_ * D + S * F_) + 4.0 * S * D)
+        ops.moe_gemm(h, 1, self.w_out, D, order, tiles, n_tiles, max_tiles, rows, y, ctx.stream)
+        return y, top
+
+    def forward(self, ctx, x, residual):
+        y, terms = self.branch(ctx, x)
+        ops.label(self.name + ".sum", terms * x.shape[0] * self.width, 4.0 * (terms + 2) * x.shape[0] * self.width)
+        ops.dyt_residual(residual, y, ctx.stream, terms=terms, token_req=ctx.token_req)
+        return residual
+
+
+register_part("feed_forward", "experts_mlp", ExpertsMLP)
 
 
 class LearnedActMLP(FeedForward):

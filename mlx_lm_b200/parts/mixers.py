@@ -283,30 +283,52 @@ class TalkingHeadsAttention(Mixer):
     * ``window``: position ``p`` sees the last ``window`` positions; ``chunk``: it sees ``j <= p`` of its own run of
       ``chunk`` positions, runs counted from position 0 of the sequence (earlier runs' pages are given back);
     * ``head_gate``: head ``h``'s output times ``sigmoid(W_g x)_h`` (``<name>.g`` ``[heads, width]``, the mixer's own
-      input), before the output projection ``<name>.o`` (bias ``<name>.o.b``).
+      input), before the output projection ``<name>.o`` (bias ``<name>.o.b``); ``column_gate``: every column of the
+      concatenated heads has a gate of its own (``<name>.g`` ``[heads * vdim, width]``);
+    * ``softcap``: scores become ``softcap * tanh(score / softcap)`` after the scale, before the softmax;
+    * ``keep_first``: beside the window, the first ``keep_first`` positions of the sequence stay visible to every later
+      position (``j <= p and (p - j < window or j < keep_first)``); their pages are never given back;
+    * ``own_kv=False``: the layer has no key and value projections; it reads the pages another layer wrote (the run
+      order points it there with ``write=False``) with its own queries, mask, scale and gate.  ``cache_window`` and
+      ``cache_keep_first`` say what the shared pages must keep when the layers that read them differ in their masks
+      (by default this layer's own ``window`` and ``keep_first``); all layers on one cache give the same.
 
-    Queries go to the kernel in float32; scores, their mix and the softmax are float32."""
+    Queries go to the kernel in float32; scores, their mix and the softmax are float32.  ``mix`` returns the output
+    projection in float32 for a block that adds it to the stream itself; ``forward`` adds it in that product's epilogue."""
     replayable = True
     kernel_libs = ("attention_wide", "attention_wide_tc", "rotary")
 
     def __init__(self, name: str, width: int, n_heads: int, n_kv_heads: int, dim: int, vdim: int, scale: float,
                  eps: float, rot_dims: int = 0, rot_base: float = 10000.0, interleaved: bool = False, bias: bool = True,
                  talk: bool = True, value_norm: bool = True, head_gate: bool = True, window: Optional[int] = None,
-                 chunk: Optional[int] = None, init: Init = Init(), bias_init: Init = Init()):
+                 chunk: Optional[int] = None, init: Init = Init(), bias_init: Init = Init(), column_gate: bool = False,
+                 softcap: float = 0.0, keep_first: int = 0, own_kv: bool = True, cache_window: Optional[int] = None,
+                 cache_keep_first: Optional[int] = None):
         if n_heads % n_kv_heads:
             raise ValueError(f"{name}: {n_heads} query heads are not a multiple of {n_kv_heads} key/value heads")
         if rot_dims % 2 or rot_dims > dim:
             raise ValueError(f"{name}: {rot_dims} rotated dimensions of {dim}")
+        if head_gate and column_gate:
+            raise ValueError(f"{name}: a gate per head or a gate per column, not both")
+        if keep_first and not window:
+            raise ValueError(f"{name}: kept first positions go with a window")
+        if not own_kv and (value_norm or rot_dims):
+            raise ValueError(f"{name}: a layer that reads another layer's pages neither rotates nor norms them")
         self.name, self.width = name, width
         self.n_heads, self.n_kv_heads, self.dim, self.vdim = n_heads, n_kv_heads, dim, vdim
+        self.column_gate, self.softcap, self.keep_first, self.own_kv = column_gate, float(softcap or 0.0), int(keep_first or 0), own_kv
+        self.cache_window = window if cache_window is None else cache_window
+        self.cache_keep_first = self.keep_first if cache_keep_first is None else int(cache_keep_first)
         self.key_row, self.value_row = (dim + 7) // 8 * 8, (vdim + 7) // 8 * 8     # rows of the pages: whole 16 bytes
         self.scale, self.eps, self.window, self.chunk = float(scale), float(eps), window, chunk
         self.rot_dims, self.rot_base, self.interleaved = rot_dims, float(rot_base), interleaved
         self.has_talk, self.value_norm, self.head_gate = talk, value_norm, head_gate
-        sources = [(f"{name}.q", n_heads * dim), (f"{name}.k", n_kv_heads * dim), (f"{name}.v", n_kv_heads * vdim)]
+        sources = [(f"{name}.q", n_heads * dim)]
+        if own_kv:
+            sources += [(f"{name}.k", n_kv_heads * dim), (f"{name}.v", n_kv_heads * vdim)]
         biases = {n: n + ".b" for n, _ in sources} if bias else None
-        if head_gate:
-            sources.append((f"{name}.g", n_heads))
+        if head_gate or column_gate:
+            sources.append((f"{name}.g", n_heads * vdim if column_gate else n_heads))
         self.proj = FusedLinear(f"{name}.qkvg", width, sources, init=init, biases=biases, bias_init=bias_init)
         self.out = Linear(f"{name}.o", n_heads * vdim, width, bias=False, weight_suffix="", init=init)
         self.has_bias, self.bias_init = bias, bias_init
@@ -316,7 +338,8 @@ class TalkingHeadsAttention(Mixer):
         return (self.proj, self.out)
 
     def cache_spec(self):
-        return PagedKVSpec(self.n_kv_heads, self.key_row, self.window, chunk=self.chunk, value_dim=self.value_row)
+        return PagedKVSpec(self.n_kv_heads, self.key_row, self.cache_window, chunk=self.chunk, value_dim=self.value_row,
+                           keep_first=self.cache_keep_first or None)
 
     def param_specs(self) -> List[ParamSpec]:
         specs = []
@@ -339,7 +362,17 @@ class TalkingHeadsAttention(Mixer):
             self.out.bias = tensors[f"{self.name}.o.b"]     # named beside the tensor, not ".bias": set once the layer is bound
 
     def forward(self, ctx, x, residual, cache):
+        return self.out.forward(ctx, self._heads_out(ctx, x, cache), residual, residual=residual)
+
+    def mix(self, ctx, x, cache, tag: str = "mix_out"):
+        o = self._heads_out(ctx, x, cache)
+        return self.out.forward(ctx, o, ctx.ws.get(tag, x.shape[0], self.width, torch.float32))
+
+    def _heads_out(self, ctx, x, cache):
         T, H, G = x.shape[0], self.n_heads, self.n_kv_heads
+        if cache.write != self.own_kv:
+            raise ops.KernelError(f"{self.name}: a layer {'with' if self.own_kv else 'without'} key and value "
+                                  f"projections {'writes its' if self.own_kv else 'only reads another layer\'s'} pages")
         n = self.proj.n_out
         proj = ctx.ws.get("attn_proj", T, (n + 7) // 8 * 8, x.dtype)[:, :n]
         self.proj.forward(ctx, x, proj)
@@ -351,14 +384,18 @@ class TalkingHeadsAttention(Mixer):
             pairs, keys = visible_pairs(ctx, self.window, self.chunk)
             ops.label(self.name + ".attention", pairs * H * (2.0 * self.dim + 2.0 * self.vdim + 2.0 * H),
                       x.element_size() * (keys * G * (self.key_row + self.value_row) + T * H * self.vdim) + 4.0 * T * H * self.dim)
-        g_off = (H + G) * self.dim + G * self.vdim
+        gate = None
+        if self.head_gate or self.column_gate:
+            g_off = self.proj.offset(f"{self.name}.g")
+            gate = proj[:, g_off:g_off + (H * self.vdim if self.column_gate else H)]
         ops.attention_wide_step(ctx, q, self.key_row, cache.k, cache.v, cache.block_table, o, self.vdim, H, self.dim,
                                 self.vdim, self.scale, window=self.window or 0, chunk=self.chunk or 0, talk=self.talk,
-                                gate=proj[:, g_off:g_off + H] if self.head_gate else None)
-        return self.out.forward(ctx, o, residual, residual=residual)
+                                gate=gate, softcap=self.softcap, keep_first=self.keep_first)
+        return o
 
     def _prepare(self, ctx, proj, cache, q) -> None:
         H, G = self.n_heads, self.n_kv_heads
+        # (a layer without key and value projections passes offsets that are never read: nothing is written)
         ops.qkv_prepare(proj, 0, H * self.dim, (H + G) * self.dim, H, G, self.dim, self.vdim, None, None, self.eps,
                         self.freq, ctx.positions, ctx.token_req, cache.block_table, cache.k, cache.v, q, cache.write,
                         ctx.status, ctx.stream, interleaved=self.interleaved,

@@ -63,7 +63,9 @@ class TokenEmbedding(Part):
         x = ctx.ws.get("residual", ctx.n_tokens, self.width, self.stream_dtype or self.table.dtype)
         table = position.embedding_table() if position is not None else None
         ops.label(self.name, ctx.n_tokens * self.width, (3 if table is not None else 2) * x.element_size() * ctx.n_tokens * self.width)
-        ops.embed_pos(ctx.tokens, ctx.positions, self.table, table, x, ctx.status, ctx.stream, scale=self.scale)
+        freq = position.embedding_frequencies() if position is not None else None
+        ops.embed_pos(ctx.tokens, ctx.positions, self.table, table, x, ctx.status, ctx.stream, scale=self.scale,
+                      freq=freq)
         return x
 
 

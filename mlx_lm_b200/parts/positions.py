@@ -38,5 +38,26 @@ class NoPosition(PositionEncoding):
     max_positions = None
 
 
+class Sinusoidal(PositionEncoding):
+    """A fixed sinusoid of the position added to the token embedding: column ``2i`` gets
+    ``sin(p * base**(-2i / width))`` and column ``2i + 1`` the cosine of the same angle.  No tensors.  The
+    frequencies are rounded to float32 once, here; the angle is a float32 product and the sum is float32, formed
+    in the embedding kernel."""
+    replayable = True
+    max_positions = None
+
+    def __init__(self, width: int, base: float = 10000.0):
+        self.width, self.base = width, float(base)
+        self.freq: Optional[torch.Tensor] = None
+
+    def bind(self, tensors, dtype, device) -> None:
+        i = torch.arange((self.width + 1) // 2, dtype=torch.float64)
+        self.freq = (self.base ** (-2.0 * i / self.width)).to(torch.float32).to(device)
+
+    def embedding_frequencies(self):
+        return self.freq
+
+
 register_part("position", "learned_absolute", LearnedAbsolute)
+register_part("position", "sinusoidal", Sinusoidal)
 register_part("position", "none", NoPosition)
