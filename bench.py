@@ -682,6 +682,40 @@ def nufetar_config(width, vocab):
             "layers": [att, lat, lat, rec, att] * 2}
 
 
+def dalorax_config(width, vocab):
+    """Ten layers of the sizes a model of this width would have: heads of 64 with a quarter as many key/value heads,
+    a window of 1024 positions beside four kept first ones, scores capped at 30; every third layer reads the pages
+    of the layer before it; feed-forwards in turn dense (about 2.7 times the width) and of 16 experts of a quarter
+    of that inner size, two a token."""
+    H = width // 64
+    inner = (width * 11 // 4 + 127) // 128 * 128
+    dense = {"ff": inner, "kind": "dense"}
+    moe = {"kind": "moe", "expert": {"ff": inner // 4}, "router": {"experts": 16, "top": 2}}
+
+    def att(mlp, kv_from=None):
+        m = {"dim": 64, "heads": H, "kv_heads": max(1, H // 4), "vdim": 64, "scale": 0.125, "softcap": 30.0,
+             "mask": {"size": 1024, "keep_first": 4}}
+        if kv_from is not None:
+            m["kv_from"] = kv_from
+        return {"type": "attention", "mlp": mlp, "mixer": m}
+    layers = []
+    for i in range(10):
+        layers.append(att(moe if i % 2 else dense, kv_from=i - 1 if i % 3 == 2 else None))
+    return {"architecture": "Dalorax", "vocab": vocab, "width": width, "logit_scale": 1.0, "norm": {"eps": 1e-5},
+            "layers": layers}
+
+
+def run_dalorax(args):
+    """The same measurements as ``--only nufetar`` for the Dalorax design, beside Nufetar (the nearest design in the
+    tree: a float32 stream, the same windowed attention part, gated feed-forwards) at equal width and as many layers."""
+    vocab = 32000
+
+    def models(width):
+        dal = dalorax_config(width, vocab)
+        return len(dal["layers"]), [("dalorax", dal), ("nufetar", nufetar_config(width, vocab))]
+    run_beside(args, "dalorax_vs_nufetar", models)
+
+
 def run_nufetar(args):
     """The same measurements as ``--only lelatar`` for the Nufetar design, beside Lelatar (the nearest design in
     the tree: a float32 stream, recurrent layers and attention layers side by side) at equal width and as many
@@ -792,9 +826,9 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration's 24 (0 = all)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--widths", default="", help="with --only lelatar / nufetar: the model widths to run, with commas (default 1024,2048)")
+    ap.add_argument("--widths", default="", help="with --only lelatar / nufetar / dalorax: the model widths to run, with commas (default 1024,2048)")
     ap.add_argument("--only", default="", choices=["", "decode", "prefill", "mixed", "timeline", "kernels", "yardstick",
-                                                   "lelatar", "nufetar"],
+                                                   "lelatar", "nufetar", "dalorax"],
                     help="run just this part and print its figures (decode / prefill: short runs for profiling; "
                          "mixed: 64 requests with prompts of 16..1024 tokens through the scheduler, 256-token portions "
                          "beside decoding requests; timeline: every kernel of one step with its start and end, "
@@ -802,7 +836,8 @@ def main():
                          "alone, with bytes, flops and the fraction of the measured peak; yardstick: torch.matmul on the "
                          "model's linear shapes, to hold the hand-written kernels against; lelatar: prefill and decode of "
                          "the Lelatar design at two widths beside GPT-2 of equal width and layer runs, with every kernel "
-                         "of both against its roofline; nufetar: the same for the Nufetar design beside Lelatar)")
+                         "of both against its roofline; nufetar: the same for the Nufetar design beside Lelatar; dalorax: the same for the Dalorax design "
+                         "beside Nufetar)")
     ap.add_argument("--prefill-prompts", type=int, default=0,
                     help="with --only prefill: 1024-token prompts in the one step (default and the contract's figure: "
                          "2); with --only timeline: the timeline of such a step instead of a decode step")
@@ -823,6 +858,9 @@ def main():
         return 0
     if a.only == "nufetar":
         run_nufetar(a)
+        return 0
+    if a.only == "dalorax":
+        run_dalorax(a)
         return 0
     run_ours(a)
     return 0

@@ -25,6 +25,10 @@
 // elements (128 bytes).  Pages that a block covers but the request does not have (beyond its last position)
 // are loaded from the request's first page instead: their scores are masked, and the values they are
 // multiplied with (by zero) must be finite.
+//
+// Options of newer designs, each an argument: `softcap` (scores become softcap * tanh(scale * s / softcap) before the
+// softmax), `keep_first` (beside a window the first so many positions of the sequence stay visible: their blocks are
+// walked first, then the window's), `gate` (every output column times the sigmoid of a bfloat16 gate column).
 #include <cuda.h>
 
 #include "common.cuh"
@@ -141,7 +145,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             const __grid_constant__ CUtensorMap map_v, const int4* __restrict__ tiles,
                             const int* __restrict__ block_table, int max_pages, int n_pages, int page, int Hq, int Hkv,
                             int window, float scale_log2e, __nv_bfloat16* out, int ldo, int* __restrict__ status,
-                            const float* __restrict__ sinks) {
+                            const float* __restrict__ sinks, int keep_first, float softcap,
+                            const __nv_bfloat16* gate, int ldg) {
   extern __shared__ uint8_t smem_raw[];
   AtSmem& sm = *reinterpret_cast<AtSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -180,7 +185,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   const int last_pos = pos0 + n_rows - 1;
   const int first_key = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
   const int kb_lo = first_key / TK, kb_hi = last_pos / TK;
-  const int n_blocks = kb_hi - kb_lo + 1;
+  // blocks with kept first positions that lie before the window's first block are walked first: block i of the walk
+  // is block kb_at(i) of the sequence
+  const int kept = keep_first < last_pos + 1 ? keep_first : last_pos + 1;
+  const int kf_blocks = (window > 0 && kept > 0) ? ((kept + TK - 1) / TK < kb_lo ? (kept + TK - 1) / TK : kb_lo) : 0;
+  const int n_blocks = kf_blocks + kb_hi - kb_lo + 1;
+  auto kb_at = [&](int i) { return i < kf_blocks ? i : kb_lo + i - kf_blocks; };
 
   if (warp == MMA_WARP) {
     // The whole warp takes part in the loads: lane s looks up the page of slot s of a block (one round of
@@ -210,14 +220,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       __syncwarp();
       if (lane < pages_per_block) tma_load_2d(dst + (size_t)lane * page * HD, map, 0, (pg * Hkv + hk) * page, bar);
     };
-    int pg_now = page_of(kb_lo);
+    int pg_now = page_of(kb_at(0));
     if (lane == 0) {
       mbar_expect_tx(&sm.q_full, TQ * HD * (uint32_t)sizeof(__nv_bfloat16));
       tma_load_2d(sm.q, &map_q, h * HD, row0, &sm.q_full);
     }
     load_pages(&map_k, sm.k, &sm.k_full, pg_now);
     load_pages(&map_v, sm.v, &sm.v_full, pg_now);
-    int pg_next = page_of(kb_lo + 1);
+    int pg_next = page_of(kb_at(1));
 
     constexpr uint32_t idesc_s = umma_idesc(TQ, TK, false);
     constexpr uint32_t idesc_o = umma_idesc(TQ, HD, true);
@@ -263,7 +273,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         issue_s();
       }
-      const int pg_after = page_of(kb_lo + i + 2);                 // its latency hides behind the wait below
+      const int pg_after = page_of(kb_at(i + 2));                 // its latency hides behind the wait below
       if (!(ok = mbar_wait_warp(&sm.o_full, ph, abort_flag))) break;    // O_b(i) is there: V and P are free
       if (more) load_pages(&map_v, sm.v, &sm.v_full, pg_next);
       pg_next = pg_after;
@@ -281,19 +291,33 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
     for (int d = 0; d < HD / 2; ++d) o[d] = 0.f;
     float m = -INFINITY, l = 0.f;   // running maximum of the row in units of the exponent; this half's running sum
+    // with a cap the scores leave it scaled: what is left for the exponent is log2(e); cap_in turns a raw score into
+    // the argument of the exponential inside tanh, 2 * scale / softcap in units of log2
+    const float cap_in = softcap > 0.f ? 2.f * scale_log2e / softcap : 0.f;
+    const float mult = softcap > 0.f ? 1.4426950408889634f : scale_log2e;
     uint8_t* p_row = reinterpret_cast<uint8_t*>(sm.p) + half * (TQ * 64 * 2) + (r >> 3) * 1024 + (r & 7) * 128;
     bool ok = true;
     for (int i = 0; i < n_blocks && ok; ++i) {
       const uint32_t ph = (uint32_t)(i & 1);
-      const int key_base = (kb_lo + i) * TK + half * 64;
+      const int kb = kb_at(i);
+      const int key_base = kb * TK + half * 64;
       if (!(ok = mbar_wait_warp(&sm.s_full, ph, abort_flag))) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       // blocks that lie wholly before the tile's first query and after every row's window floor need no mask
-      const bool open = (kb_lo + i) * TK + TK - 1 <= pos0 && (window <= 0 || (kb_lo + i) * TK >= last_pos - window + 1);
+      const bool open = kb * TK + TK - 1 <= pos0 &&
+                        (window <= 0 || kb * TK >= last_pos - window + 1 || kb * TK + TK - 1 < keep_first);
       uint32_t s0[32], s1[32];
       tmem_ld32(t_s, s0);
       tmem_ld32(t_s + 32u, s1);
       tmem_wait_ld();
+      if (softcap > 0.f) {   // s <- softcap * tanh(scale * s / softcap), tanh(x) = 1 - 2 / (exp(2x) + 1)
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          const float t0 = fast_exp2(__uint_as_float(s0[e]) * cap_in), t1 = fast_exp2(__uint_as_float(s1[e]) * cap_in);
+          s0[e] = __float_as_uint(softcap - 2.f * softcap * __fdividef(1.f, t0 + 1.f));
+          s1[e] = __float_as_uint(softcap - 2.f * softcap * __fdividef(1.f, t1 + 1.f));
+        }
+      }
       float mx = -INFINITY;
       if (open) {
 #pragma unroll
@@ -302,8 +326,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
         for (int e = 0; e < 32; ++e) {
           const int k0 = key_base + e, k1 = key_base + 32 + e;
-          if (!(k0 <= pos && k0 >= lo)) s0[e] = 0xff800000u;   // -inf: masked here once, exp2 gives 0 below
-          if (!(k1 <= pos && k1 >= lo)) s1[e] = 0xff800000u;
+          if (!(k0 <= pos && (k0 >= lo || k0 < keep_first))) s0[e] = 0xff800000u;   // -inf: masked here once, exp2 gives 0 below
+          if (!(k1 <= pos && (k1 >= lo || k1 < keep_first))) s1[e] = 0xff800000u;
           mx = fmaxf(mx, fmaxf(__uint_as_float(s0[e]), __uint_as_float(s1[e])));
         }
       }
@@ -312,7 +336,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       if (lane == 0) mbar_arrive(&sm.x_full);
       if (!(ok = mbar_wait_warp(&sm.x_full, ph, abort_flag))) break;
       mx = fmaxf(mx, sm.row_max[half ^ 1][r]);
-      const float m_new = fmaxf(m, mx * scale_log2e);   // scale > 0
+      const float m_new = fmaxf(m, mx * mult);   // scale > 0
       const float base = m_new == -INFINITY ? 0.f : m_new;
       const float corr = fast_exp2(m - base);           // 2^-inf = 0
       m = m_new;
@@ -323,7 +347,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
         for (int e = 0; e < 32; e += 2) {
           const float a0 = __uint_as_float(c == 0 ? s0[e] : s1[e]), a1 = __uint_as_float(c == 0 ? s0[e + 1] : s1[e + 1]);
-          const float p0 = fast_exp2(fmaf(a0, scale_log2e, -base)), p1 = fast_exp2(fmaf(a1, scale_log2e, -base));
+          const float p0 = fast_exp2(fmaf(a0, mult, -base)), p1 = fast_exp2(fmaf(a1, mult, -base));
           sum += p0 + p1;
           const __nv_bfloat162 pr = __floats2bfloat162_rn(p0, p1);
           packed[e >> 1] = *reinterpret_cast<const uint32_t*>(&pr);
@@ -369,6 +393,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         float v8[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) v8[e] = o[d + e] * inv;
+        if (gate) {
+          float g8[8];
+          unpack8(*reinterpret_cast<const uint4*>(gate + (size_t)(row0 + r) * ldg + h * HD + half * (HD / 2) + d), g8);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) v8[e] *= 1.f / (1.f + expf(-g8[e]));
+        }
         *reinterpret_cast<uint4*>(dst + d) = pack8(v8);
       }
     }
@@ -409,8 +439,12 @@ MLXB_EXPORT int mlxb_attention_prefill_tc(const void* q, int ldq, int n_tokens, 
                                           const int* block_table, int max_pages, int n_pages, int page, int Hq,
                                           int Hkv, int Dh, int window, float scale, const void* k_pool,
                                           const void* v_pool, void* out, int ldo, int* status, const float* sinks,
+                                          int keep_first, float softcap, const void* gate, int ldg,
                                           cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
+  if (keep_first < 0 || softcap < 0.f || (gate && ((ldg & 7) || ((uintptr_t)gate & 15))))
+    return mlxb_fail(MLXB_BAD_ARG, "attention (portions, tcgen05): %d kept positions, cap %g, gate rows at stride %d",
+                     keep_first, (double)softcap, ldg);
   if (Dh != HD) return mlxb_fail(MLXB_BAD_ARG, "attention (portions, tcgen05): head size %d, this kernel takes %d", Dh, HD);
   if (page < 8 || page > TK || (page & (page - 1)))
     return mlxb_fail(MLXB_BAD_ARG, "attention (portions, tcgen05): page size %d (a power of two from 8 to %d)", page, TK);
@@ -434,6 +468,7 @@ MLXB_EXPORT int mlxb_attention_prefill_tc(const void* q, int ldq, int n_tokens, 
   }
   launch_pdl(attention_prefill_tc_kernel, dim3(n_tiles, Hq), dim3(AT_THREADS), smem, stream, mq, mk, mv,
              (const int4*)tiles, block_table, max_pages, n_pages, page, Hq, Hkv, window,
-             scale * 1.4426950408889634f, (__nv_bfloat16*)out, ldo, status, sinks);
+             scale * 1.4426950408889634f, (__nv_bfloat16*)out, ldo, status, sinks, window > 0 ? keep_first : 0, softcap,
+             (const __nv_bfloat16*)gate, ldg);
   return mlxb_check_launch("attention (portions, tcgen05)");
 }

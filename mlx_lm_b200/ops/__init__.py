@@ -1262,6 +1262,48 @@ def moe_gemm(a, a_div: int, w, n_out: int, sorted_slots, tile_info, n_tiles, max
           int(max_tiles), int(tile_rows), _p(sel_weight), _p(out), _rows(out, "moe_gemm out"), stream)
 
 
+def moe_tc05_tile_rows() -> int:
+    """Slots a tile of the experts' products on the 5th-generation tensor cores takes (``moe_gemm_tc05``)."""
+    f, _ = _fn("moe_tcgen05", "mlxb_moe_tc05_tile_rows", [])
+    return int(f())
+
+
+def moe_gather(src, a_div: int, sorted_slots, tile_info, n_tiles, max_tiles: int, dst, stream) -> None:
+    """``dst[i] = src[sorted_slots[i] // a_div]`` for every place of the plan's tiles: the slots' rows in the plan's
+    order, so that one expert's rows lie together.  bfloat16, whole 16 bytes a row."""
+    _need(src, torch.bfloat16, "moe_gather src")
+    _need(dst, torch.bfloat16, "moe_gather dst")
+    if src.shape[1] != dst.shape[1]:
+        raise KernelError(f"moe_gather: src {tuple(src.shape)}, dst {tuple(dst.shape)}")
+    _call("moe_tcgen05", "mlxb_moe_gather", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p,
+                                             c_int, c_void_p],
+          _p(src), _rows(src, "moe_gather src"), int(a_div), _p(sorted_slots), _p(tile_info), _p(n_tiles), int(max_tiles),
+          src.shape[1], _p(dst), _rows(dst, "moe_gather dst"), stream)
+
+
+def moe_gemm_tc05(a, w, n_out: int, sorted_slots, tile_info, n_tiles, max_tiles: int, out, status, stream,
+                  sel_weight=None, gated: bool = False) -> None:
+    """The experts' products over a plan of ``moe_tc05_tile_rows()``-slot tiles on the 5th-generation tensor cores.
+    ``a``: bfloat16 rows IN THE PLAN'S ORDER (``moe_gather``, or the gated product's own result); ``w [E, n_out, K]``.
+    ``gated``: ``w [E, 2 n_out, K]`` holds gate rows then up rows and ``out`` (bfloat16, in the plan's order) is
+    ``silu(s g) * (s u)`` with ``s`` the slot's routing weight; else ``out`` (float32) gets the product of the row at
+    place ``i`` in row ``sorted_slots[i]``.  ``status``: receives a bit if a bounded wait in the kernel gives up."""
+    _need(a, torch.bfloat16, "moe_gemm_tc05 a")
+    _need(w, torch.bfloat16, "moe_gemm_tc05 w")
+    _need(out, torch.bfloat16 if gated else torch.float32, "moe_gemm_tc05 out")
+    _need(status, torch.int32, "moe_gemm_tc05 status")
+    E, NW, K = w.shape
+    if NW != (2 if gated else 1) * n_out or a.shape[1] != K or out.shape[1] != n_out or not w.is_contiguous():
+        raise KernelError(f"moe_gemm_tc05: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    if gated:
+        _need(sel_weight, torch.float32, "moe_gemm_tc05 sel_weight")
+    _call("moe_tcgen05", "mlxb_moe_gemm_tc05", [c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
+                                                c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p],
+          int(bool(gated)), _p(a), _rows(a, "moe_gemm_tc05 a"), a.shape[0], _p(w), E, NW, n_out, K, _p(sorted_slots),
+          _p(tile_info), _p(n_tiles), int(max_tiles), _p(sel_weight), _p(out), _rows(out, "moe_gemm_tc05 out"), _p(status),
+          stream)
+
+
 # --------------------------------------------------------------------------
 # small row-wise kernels (csrc/elementwise.cu)
 

@@ -89,11 +89,12 @@ class ExpertsMLP(FeedForward):
 
     The experts' weights are stacked at bind time (``[E, 2 inner, width]`` gate rows then up rows, ``[E, width,
     inner]``); a step routes (``ops.moe_route``), sorts its (token, choice) slots by expert into tiles
-    (``ops.moe_plan``) and runs two products over the tiles (``ops.moe_gemm``), the gated unit in the first one's
-    epilogue.  ``branch`` returns one float32 row per slot, ``top`` rows a token, which the caller sums in the order
+    (``ops.moe_plan``) and runs two products over the tiles, the gated unit in the first one's epilogue: ``ops.moe_gemm``
+    for the few slots of decoding steps, ``ops.moe_gather`` and ``ops.moe_gemm_tc05`` (tcgen05, TMA) for many.  ``branch`` returns one float32 row per slot, ``top`` rows a token, which the caller sums in the order
     of the choices; ``forward`` adds them to a float32 stream."""
     replayable = True
-    kernel_libs = ("moe", "dyt")
+    kernel_libs = ("moe", "moe_tcgen05", "dyt")
+    MANY_SLOTS = 512     # (token, choice) slots of a step from which the 128-row tiles pay
 
     def __init__(self, name: str, width: int, inner: int, n_experts: int, top: int, score: str = "sigmoid",
                  renormalize: bool = False, scale_input: bool = True, router_name: str = "router",
@@ -138,17 +139,30 @@ class ExpertsMLP(FeedForward):
         ops.label(self.name + ".route", 8.0 * T * E, 4.0 * T * E + 8.0 * S)
         ops.moe_route(logits, ctx.token_req, top, sel_e, sel_w, ctx.stream, score=self.score, renormalize=self.renormalize)
         tc = x.dtype == torch.bfloat16 and D % 8 == 0 and F_ % 8 == 0 and x.stride(0) % 8 == 0
-        rows = ops.moe_tile_rows(tc)
+        # many slots: tiles of 128 rows of one expert on the 5th-generation tensor cores, the rows gathered in the
+        # plan's order first; few slots (decoding): tiles of 64 through the sorted list, or the CUDA cores
+        many = tc and S >= self.MANY_SLOTS
+        rows = ops.moe_tc05_tile_rows() if many else ops.moe_tile_rows(tc)
         max_tiles = ops.moe_max_tiles(S, E, rows)
         order = ctx.ws.flat("moe_sorted", S, torch.int32)
         tiles = ctx.ws.flat("moe_tiles", 3 * max_tiles + 1, torch.int32)
         n_tiles = tiles[3 * max_tiles:]
         ops.moe_plan(sel_e, S, E, rows, order, tiles, n_tiles, ctx.stream)
         h = ctx.ws.get("moe_hidden", S, F_, x.dtype)
+        y = ctx.ws.get("moe_out", S, D, torch.float32)
         es = x.element_size()
+        if many:
+            xs = ctx.ws.get("moe_rows", S, D, x.dtype)
+            ops.label(self.name + ".gather", 0.0, es * (T + S) * D)
+            ops.moe_gather(x, top, order, tiles, n_tiles, max_tiles, xs, ctx.stream)
+            ops.label(self.name + ".experts.in", 4.0 * S * D * F_, es * (min(E, S) * 2 * F_ * D + S * D + S * F_))
+            ops.moe_gemm_tc05(xs, self.w_in, F_, order, tiles, n_tiles, max_tiles, h, ctx.status, ctx.stream,
+                              sel_weight=sel_w, gated=True)
+            ops.label(self.name + ".experts.out", 2.0 * S * D * F_, es * (min(E, S) * F_ * D + S * F_) + 4.0 * S * D)
+            ops.moe_gemm_tc05(h, self.w_out, D, order, tiles, n_tiles, max_tiles, y, ctx.status, ctx.stream)
+            return y, top
         ops.label(self.name + ".experts.in", 4.0 * S * D * F_, es * (min(E, S) * 2 * F_ * D + T * D + S * F_))
         ops.moe_gemm(x, top, self.w_in, F_, order, tiles, n_tiles, max_tiles, rows, h, ctx.stream, sel_weight=sel_w, gated=True)
-        y = ctx.ws.get("moe_out", S, D, torch.float32)
         ops.label(self.name + ".experts.out", 2.0 * S * D * F_, es * (min(E, S) * F_ * D + S * F_) + 4.0 * S * D)
         ops.moe_gemm(h, 1, self.w_out, D, order, tiles, n_tiles, max_tiles, rows, y, ctx.stream)
         return y, top

@@ -57,13 +57,50 @@ ONLY_EXPERTS = model(64, 48, [attention(dim=16, heads=2, kv_heads=1, vdim=16, si
 ALL = {"A": CONFIG_A, "B": CONFIG_B, "W": CONFIG_W, "odd": CONFIG_ODD, "attention": ONLY_ATTENTION, "experts": ONLY_EXPERTS}
 
 
-def make_dir(path, config, seed, edit=None):
-    """A model folder with random weights; ``edit(tensors)`` may change them (float32 in, rounded to bfloat16 again)."""
+CODE_COLUMNS = 5
+
+
+def decisive_routers(w, config, seed, gap=0.1):
+    """Routers that never face a close call, so that bfloat16 rounding cannot send a token to another expert than
+    float64 does.  The first few columns of the embedding hold +-30: the norms' tanh saturates there whatever the
+    layers add, so the feed-forward's input has one of 2^CODE_COLUMNS fixed patterns in these columns.  The routers
+    read only these columns and are drawn again until, for every pattern, the last chosen expert's logit is ``gap``
+    above the next one's.  The model's last norm is zero in these columns, so they do not reach the logits."""
+    g = torch.Generator().manual_seed(1000 + seed)
+    n = CODE_COLUMNS
+    w["embed"][:, :n] = 30.0 * (torch.randint(0, 2, (config["vocab"], n), generator=g) * 2 - 1).float()
+    w["final.norm"][:n] = 0.0
+    w["final.norm.b"][:n] = 0.0
+    signs = torch.tensor([[1.0 if (p >> c) & 1 else -1.0 for c in range(n)] for p in range(2 ** n)])
+    rounded = lambda t: t.to(torch.bfloat16).float()
+    for i, layer in enumerate(config["layers"]):
+        mlp = layer.get("mlp")
+        if mlp is None or mlp["kind"] != "moe":
+            continue
+        E, top = mlp["router"]["experts"], mlp["router"]["top"]
+        h = rounded(signs * torch.sign(w[f"l{i}.norm2.alpha"]) * rounded(w[f"l{i}.norm2"][:n]) + rounded(w[f"l{i}.norm2.b"][:n]))
+        for _ in range(100000):
+            r = rounded(2.0 * torch.randn(E, n, generator=g))
+            z = (h @ r.T).sort(dim=-1, descending=True).values
+            if top == E or float((z[:, top - 1] - z[:, top]).min()) > gap:
+                break
+        else:
+            raise RuntimeError(f"no decisive router for layer {i}")
+        w[f"l{i}.mlp.router"] = torch.zeros_like(w[f"l{i}.mlp.router"])
+        w[f"l{i}.mlp.router"][:, :n] = r
+
+
+def make_dir(path, config, seed, edit=None, decisive=True):
+    """A model folder with random weights; ``edit(tensors)`` may change them (float32 in, rounded to bfloat16 again).
+    ``decisive``: routers without close calls (``decisive_routers``); without it they are as random as the rest,
+    which suits float32 runs only."""
     from mlx_lm_b200.weights import write_random_model
 
     write_random_model(str(path), copy.deepcopy(config), seed)
     file = os.path.join(str(path), "model.safetensors")
     w = {k: v.float() for k, v in load_file(file).items()}
+    if decisive:
+        decisive_routers(w, config, seed)
     if edit is not None:
         edit(w)
     save_file({k: v.to(torch.bfloat16).contiguous() for k, v in w.items()}, file)

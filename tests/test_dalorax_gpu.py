@@ -40,7 +40,7 @@ def test_whole_prompts(name, dtype, tmp_path):
     """One step per prompt, all logits: also the first tokens of a sequence (lengths 1, 2, 3: the first window is
     not full, kept positions and window overlap)."""
     config = CONFIGS[name]
-    weights = make_dir(tmp_path, config, seed=11)
+    weights = make_dir(tmp_path, config, seed=11, decisive=dtype == "bfloat16")
     reqs = {f"r{n}": tokens(n, config["vocab"], n) for n in (1, 2, 3, 37, 150)}
     tr = Trace()
     for rid, toks in reqs.items():
@@ -58,7 +58,7 @@ def test_every_cutting_gives_the_same_logits(name, dtype, tmp_path):
     more than 128); mixed batches of unequal requests in a pool with three slots and few pages, so that both are used
     again by later requests."""
     config = CONFIGS[name]
-    weights = make_dir(tmp_path, config, seed=5)
+    weights = make_dir(tmp_path, config, seed=5, decisive=dtype == "bfloat16")
     V = config["vocab"]
     reqs = {"a": tokens(70, V, 1), "b": tokens(131, V, 2), "c": tokens(23, V, 3), "d": tokens(300, V, 4), "e": tokens(5, V, 5)}
     tr = Trace()
@@ -198,7 +198,7 @@ def test_long_decoding(dtype, tmp_path):
     """A short prompt and then 500 tokens one by one beside a second request: windows pass over decoded tokens many
     times, pages behind the windows are given back and taken again while those of the kept positions stay."""
     config = CONFIG_A
-    weights = make_dir(tmp_path, config, seed=8)
+    weights = make_dir(tmp_path, config, seed=8, decisive=dtype == "bfloat16")
     V = config["vocab"]
     reqs = {"a": tokens(510, V, 1), "b": tokens(200, V, 2)}
     ref = reference(config, weights, reqs)

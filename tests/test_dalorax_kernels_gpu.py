@@ -304,3 +304,59 @@ def test_experts_products(act, T, D, F, E, top):
         assert float((h[s].double().cpu() - hs).abs().max()) < tol * max(1.0, float(hs.abs().max())), ("hidden", s)
         want = w_out[e].double() @ h[s].double().cpu()
         assert float((y[s].double().cpu() - want).abs().max()) < tol * max(1.0, float(want.abs().max())), ("out", s)
+
+
+@pytest.mark.parametrize("T,D,F,E,top", [(300, 96, 128, 5, 3), (700, 128, 72, 16, 2), (5, 64, 64, 3, 2), (260, 200, 136, 7, 1),
+                                          (1024, 256, 192, 4, 2), (40, 64, 8, 30, 4)])
+def test_experts_products_on_tcgen05(T, D, F, E, top):
+    """Tiles of 128 slots of one expert: the rows gathered in the plan's order, the gated product's result in that
+    order too, the second product's rows back at the slots' own places.  Inner sizes that are no multiple of the
+    64-column stages or of the 64 / 128 output columns a CTA makes, experts without a slot, one expert with many
+    tiles, a row that pads the step."""
+    from mlx_lm_b200 import ops
+    torch.manual_seed(T + D + F + E)
+    S = T * top
+    act = torch.bfloat16
+    x = torch.randn(T, D).to(act)
+    w_in = (torch.randn(E, 2 * F, D) * D ** -0.5).to(act)
+    w_out = (torch.randn(E, D, F) * F ** -0.5).to(act)
+    sel_e = torch.stack([torch.randperm(E)[:top] for _ in range(T)]).to(torch.int32)
+    if T > 600:
+        sel_e[: T // 2] = torch.tensor([E - 1, 1][:top], dtype=torch.int32)     # one expert with several full tiles
+    if T > 20:
+        sel_e[11] = -1
+    sel_w = torch.rand(S) + 0.2
+    rows = ops.moe_tc05_tile_rows()
+    max_tiles = ops.moe_max_tiles(S, E, rows)
+    order = torch.full((S,), -1, dtype=torch.int32, device=DEV)
+    tiles = torch.full((3 * max_tiles + 1,), -1, dtype=torch.int32, device=DEV)
+    n_tiles = tiles[3 * max_tiles:]
+    ops.moe_plan(sel_e.flatten().to(DEV), S, E, rows, order, tiles, n_tiles, stream())
+    xd, wi, wo = x.to(DEV), w_in.to(DEV), w_out.to(DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    xs = torch.full((S, D), float("nan"), dtype=act, device=DEV)
+    ops.moe_gather(xd, top, order, tiles, n_tiles, max_tiles, xs, stream())
+    h = torch.full((S, F), 7.0, dtype=act, device=DEV)
+    ops.moe_gemm_tc05(xs, wi, F, order, tiles, n_tiles, max_tiles, h, status, stream(), sel_weight=sel_w.to(DEV), gated=True)
+    y = torch.full((S, D), 7.0, device=DEV)
+    ops.moe_gemm_tc05(h, wo, D, order, tiles, n_tiles, max_tiles, y, status, stream())
+    assert int(status.item()) == 0
+    flat = sel_e.flatten()
+    live = int((flat >= 0).sum())
+    place = order.cpu().tolist()
+    assert sorted(place[:live]) == [s for s in range(S) if flat[s] >= 0]
+    assert bool((h[live:] == 7.0).all())
+    xsc, hc, yc = xs.cpu(), h.double().cpu(), y.double().cpu()
+    tol = 3e-2
+    for i, s in enumerate(place[:live]):
+        e = int(flat[s])
+        assert torch.equal(xsc[i], x[s // top])
+        xv = sel_w[s].double() * x[s // top].double()
+        g, u = w_in[e, :F].double() @ xv, w_in[e, F:].double() @ xv
+        hs = g / (1 + torch.exp(-g)) * u
+        assert float((hc[i] - hs).abs().max()) < tol * max(1.0, float(hs.abs().max())), ("hidden", s)
+        want = w_out[e].double() @ hc[i]
+        assert float((yc[s] - want).abs().max()) < tol * max(1.0, float(want.abs().max())), ("out", s)
+    for s in range(S):
+        if flat[s] < 0:
+            assert bool((y[s] == 7.0).all())
