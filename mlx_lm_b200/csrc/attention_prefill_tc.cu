@@ -23,8 +23,9 @@
 // Every mbarrier wait is bounded; a wait that gives up sets an abort flag that all roles see, the CTA frees
 // its tensor memory and reports MLXB_ST_WAIT_TIMEOUT.  TMA coordinates: x is always 0 or a multiple of 64
 // elements (128 bytes).  Pages that a block covers but the request does not have (beyond its last position)
-// are loaded from the request's first page instead: their scores are masked, and the values they are
-// multiplied with (by zero) must be finite.
+// or that no query of the tile can see (behind the window: the cache may have given them back) are loaded from the
+// page of the tile's first query instead: their scores are masked, and the values they are multiplied with (by zero)
+// must be finite.
 //
 // Options of newer designs, each an argument: `softcap` (scores become softcap * tanh(scale * s / softcap) before the
 // softmax), `keep_first` (beside a window the first so many positions of the sequence stay visible: their blocks are
@@ -187,7 +188,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   const int kb_lo = first_key / TK, kb_hi = last_pos / TK;
   // blocks with kept first positions that lie before the window's first block are walked first: block i of the walk
   // is block kb_at(i) of the sequence
-  const int kept = keep_first < last_pos + 1 ? keep_first : last_pos + 1;
+  const int kept = window > 0 ? (keep_first < last_pos + 1 ? keep_first : last_pos + 1) : 0;
   const int kf_blocks = (window > 0 && kept > 0) ? ((kept + TK - 1) / TK < kb_lo ? (kept + TK - 1) / TK : kb_lo) : 0;
   const int n_blocks = kf_blocks + kb_hi - kb_lo + 1;
   auto kb_at = [&](int i) { return i < kf_blocks ? i : kb_lo + i - kf_blocks; };
@@ -199,7 +200,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int* bt = block_table + (size_t)req * max_pages;
     const int shift = __ffs(page) - 1;
     const int pages_per_block = TK / page;
-    int first_page = bt[0];
+    // Pages that a block covers but no query of the tile can see (beyond the last position, or behind the window and
+    // not among the kept first positions: the cache may have given those back) are loaded from the page of the tile's
+    // first query instead, which this step has written.
+    int first_page = (pos0 >> shift) < max_pages ? bt[pos0 >> shift] : -1;
     if (first_page < 0 || first_page >= n_pages) {
       if (lane == 0) atomicOr(status, first_page < 0 ? MLXB_ST_POSITION_RANGE : MLXB_ST_PAGE_RANGE);
       first_page = 0;
@@ -207,7 +211,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     auto page_of = [&](int kb) {   // the page this lane copies for block kb (lanes >= pages_per_block: unused)
       const int key0 = kb * TK + lane * page;
       int pg = first_page;
-      if (lane < pages_per_block && kb <= kb_hi && key0 <= last_pos) {
+      if (lane < pages_per_block && kb <= kb_hi && key0 <= last_pos && (key0 + page > first_key || key0 < kept)) {
         const int lp = key0 >> shift;
         const int id = lp < max_pages ? bt[lp] : -1;
         if (id < 0 || id >= n_pages) atomicOr(status, id < 0 ? MLXB_ST_POSITION_RANGE : MLXB_ST_PAGE_RANGE);

@@ -13,7 +13,8 @@
 //             makes of the expert's input scaled by w (the products are linear in it, so w is applied to the float32
 //             sums instead of to the rounded input).  bfloat16 runs on tensor cores (mma.sync m16n8k16, float32
 //             accumulation; 64 x 64 tiles, 16-byte cp.async in two stages), float32 (and inner sizes that are no
-//             multiple of 8) on the CUDA cores with float32 FMAs in the order of k.
+//             multiple of 8) on the CUDA cores with float32 FMAs in the order of k.  A step of a few tokens (decoding)
+//             takes tiles of 4 slots and a warp per output column instead (moe_rows_kernel).
 // A slot's result does not depend on which tile it lands in or on its place there: every output element is a sum over
 // k in a fixed order.  The sum over a token's choices is taken by the caller in the order of the choices.
 #include "common.cuh"
@@ -202,6 +203,89 @@ moe_gemm_simt_kernel(const T* A, int lda, int a_div, const T* __restrict__ W, lo
   }
 }
 
+// ---------------------------------------------------------------- few slots (decoding): bfloat16, K a multiple of 8
+// A tile is up to MV_ROWS slots of one expert.  The CTA keeps their rows in shared memory; a warp takes an output
+// column at a time, reads its row of W (and, gated, the up row of the same column) once with 16 bytes a lane, and
+// forms the column's sum for every slot of the tile: lanes over k, then a butterfly over the lanes.  The weights are
+// streamed by many small CTAs with all of a row's loads in flight, which is what a step of a few tokens needs.
+constexpr int MV_ROWS = 4, MV_COLS = 32, MV_THREADS = 256;
+
+template <typename TO, bool GATED>
+__global__ void __launch_bounds__(MV_THREADS)
+moe_rows_kernel(const __nv_bfloat16* A, int lda, int a_div, const __nv_bfloat16* __restrict__ W, long long w_stride, int N,
+                int K, const int* sorted, const int* tile_info, const int* n_tiles, const float* sel_weight,
+                TO* __restrict__ out, int ldo) {
+  extern __shared__ uint4 mv_rows[];          // [MV_ROWS][K / 8]
+  __shared__ int sSlot[MV_ROWS];
+  pdl_wait();
+  pdl_trigger();
+  A = after_wait(A);
+  sorted = after_wait(sorted);
+  tile_info = after_wait(tile_info);
+  n_tiles = after_wait(n_tiles);
+  sel_weight = after_wait(sel_weight);
+  const int tile = blockIdx.x;
+  if (tile >= n_tiles[0]) return;
+  const int e = tile_info[3 * tile], first = tile_info[3 * tile + 1], rows = tile_info[3 * tile + 2];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int k8 = K >> 3;
+  if (tid < MV_ROWS) sSlot[tid] = tid < rows ? sorted[first + tid] : -1;
+  __syncthreads();
+  for (int x = tid; x < MV_ROWS * k8; x += MV_THREADS) {
+    const int rr = x / k8, c = x - rr * k8;
+    const int slot = sSlot[rr];
+    mv_rows[x] = slot >= 0 ? reinterpret_cast<const uint4*>(A + (size_t)(slot / a_div) * lda)[c] : make_uint4(0u, 0u, 0u, 0u);
+  }
+  __syncthreads();
+  const __nv_bfloat16* We = W + (size_t)e * w_stride;
+#pragma unroll 1
+  for (int j = 0; j < MV_COLS / 8; ++j) {
+    const int n = blockIdx.y * MV_COLS + j * 8 + warp;
+    if (n >= N) continue;
+    const uint4* wg = reinterpret_cast<const uint4*>(We + (size_t)n * K);
+    const uint4* wu = reinterpret_cast<const uint4*>(We + (size_t)(N + n) * K);
+    float acc[GATED ? 2 : 1][MV_ROWS];
+#pragma unroll
+    for (int h = 0; h < (GATED ? 2 : 1); ++h)
+#pragma unroll
+      for (int rr = 0; rr < MV_ROWS; ++rr) acc[h][rr] = 0.f;
+#pragma unroll 4
+    for (int c = lane; c < k8; c += 32) {
+      float g[8], u[8];
+      unpack8(wg[c], g);
+      if (GATED) unpack8(wu[c], u);
+#pragma unroll
+      for (int rr = 0; rr < MV_ROWS; ++rr) {
+        float a[8];
+        unpack8(mv_rows[rr * k8 + c], a);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          acc[0][rr] = fmaf(a[i], g[i], acc[0][rr]);
+          if (GATED) acc[1][rr] = fmaf(a[i], u[i], acc[1][rr]);
+        }
+      }
+    }
+#pragma unroll
+    for (int h = 0; h < (GATED ? 2 : 1); ++h)
+#pragma unroll
+      for (int rr = 0; rr < MV_ROWS; ++rr) acc[h][rr] = warp_sum(acc[h][rr]);
+    if (lane < MV_ROWS) {
+      const int slot = sSlot[lane];
+      if (slot >= 0) {
+        float v = 0.f, v2 = 0.f;
+#pragma unroll
+        for (int rr = 0; rr < MV_ROWS; ++rr)
+          if (rr == lane) { v = acc[0][rr]; v2 = acc[GATED ? 1 : 0][rr]; }
+        if (GATED) {
+          const float w = sel_weight[slot];
+          v = silu_f(w * v) * (w * v2);
+        }
+        out[(size_t)slot * ldo + n] = from_f<TO>(v);
+      }
+    }
+  }
+}
+
 // ---------------------------------------------------------------- tensor cores: bfloat16, K a multiple of 8
 constexpr int MG_BM = 64, MG_BN = 64, MG_BK = 32, MG_THREADS = 128, MG_LD = MG_BK + 8;
 
@@ -316,8 +400,9 @@ moe_gemm_tc_kernel(const __nv_bfloat16* A, int lda, int a_div, const __nv_bfloat
 // A: `dtype` [*, lda]; W: `dtype` [E][(gated ? 2 : 1) * N][K] at w_stride elements an expert; out: `dtype`, or float32
 // with out_f32, [S, ldo]; max_tiles: the tiles the plan had room for (the grid); tile_rows: what the plan was made with,
 // mlxb_moe_tile_rows(1) for the tensor-core kernel (bfloat16, every inner size a multiple of 8) or
-// mlxb_moe_tile_rows(0) for the kernel on the CUDA cores; the products of one feed-forward share a plan.
-MLXB_EXPORT int mlxb_moe_tile_rows(int tensor_cores) { return tensor_cores ? MG_BM : MS_BM; }
+// mlxb_moe_tile_rows(0) for the kernel on the CUDA cores, mlxb_moe_tile_rows(2) for the kernel for few slots (bfloat16,
+// inner sizes multiples of 8 up to 6144); the products of one feed-forward share a plan.
+MLXB_EXPORT int mlxb_moe_tile_rows(int tensor_cores) { return tensor_cores == 2 ? MV_ROWS : tensor_cores ? MG_BM : MS_BM; }
 
 MLXB_EXPORT int mlxb_moe_gemm(int dtype, int out_f32, int gated, const void* A, int lda, int a_div, const void* W,
                               long long w_stride, int N, int K, const int* sorted, const int* tile_info,
@@ -325,7 +410,8 @@ MLXB_EXPORT int mlxb_moe_gemm(int dtype, int out_f32, int gated, const void* A, 
                               int ldo, cudaStream_t stream) {
   if (max_tiles <= 0) return 0;
   if (N <= 0 || K <= 0 || a_div <= 0 || lda < K || ldo < N || (gated && !sel_weight) ||
-      (tile_rows != MG_BM && tile_rows != MS_BM) || (tile_rows == MG_BM && dtype != MLXB_BF16))
+      (tile_rows != MG_BM && tile_rows != MS_BM && tile_rows != MV_ROWS) ||
+      ((tile_rows == MG_BM || tile_rows == MV_ROWS) && dtype != MLXB_BF16))
     return mlxb_fail(MLXB_BAD_ARG, "moe_gemm: %d x %d, strides %d / %d, tiles of %d rows", N, K, lda, ldo, tile_rows);
 #define MOE_SIMT(T, TO, G)                                                                                             \
   launch_pdl(moe_gemm_simt_kernel<T, TO, G>, dim3(max_tiles, (N + MS_BN - 1) / MS_BN), dim3(MS_THREADS), 0, stream,    \
@@ -338,9 +424,19 @@ MLXB_EXPORT int mlxb_moe_gemm(int dtype, int out_f32, int gated, const void* A, 
     if (gated) MOE_SIMT(float, float, true); else MOE_SIMT(float, float, false);
   } else if (dtype == MLXB_BF16) {
     const bool tc = K % 8 == 0 && lda % 8 == 0 && (((uintptr_t)A | (uintptr_t)W) & 15) == 0 && w_stride % 8 == 0;
-    if (tile_rows == MG_BM && !tc)
+    if ((tile_rows == MG_BM || tile_rows == MV_ROWS) && !tc)
       return mlxb_fail(MLXB_BAD_ARG, "moe_gemm: rows of %d elements at stride %d are not in whole 16 bytes", K, lda);
-    if (tile_rows == MG_BM) {
+    if (tile_rows == MV_ROWS) {
+      const size_t smem = (size_t)MV_ROWS * K * sizeof(__nv_bfloat16);
+      if (smem > 48 * 1024) return mlxb_fail(MLXB_BAD_ARG, "moe_gemm (few slots): rows of %d elements", K);
+#define MOE_ROWS(TO, G)                                                                                                \
+  launch_pdl(moe_rows_kernel<TO, G>, dim3(max_tiles, (N + MV_COLS - 1) / MV_COLS), dim3(MV_THREADS), smem, stream,     \
+             (const __nv_bfloat16*)A, lda, a_div, (const __nv_bfloat16*)W, w_stride, N, K, sorted, tile_info, n_tiles, \
+             sel_weight, (TO*)out, ldo)
+      if (gated) { if (out_f32) MOE_ROWS(float, true); else MOE_ROWS(__nv_bfloat16, true); }
+      else { if (out_f32) MOE_ROWS(float, false); else MOE_ROWS(__nv_bfloat16, false); }
+#undef MOE_ROWS
+    } else if (tile_rows == MG_BM) {
       if (gated) { if (out_f32) MOE_TC(float, true); else MOE_TC(__nv_bfloat16, true); }
       else { if (out_f32) MOE_TC(float, false); else MOE_TC(__nv_bfloat16, false); }
     } else {

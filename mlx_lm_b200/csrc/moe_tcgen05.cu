@@ -54,11 +54,21 @@ __global__ void moe_gather_kernel(const __nv_bfloat16* src, int lds, int a_div, 
   if (t >= after_wait(n_tiles)[0]) return;
   const int first = tile_info[3 * t + 1], cnt = tile_info[3 * t + 2];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
-  for (int r = warp; r < cnt; r += warps) {
+  // the tile's rows are spread over the CTAs of a grid column; a lane has up to four 16-byte pieces of a row in flight
+  for (int r = blockIdx.y * warps + warp; r < cnt; r += gridDim.y * warps) {
     const int slot = sorted[first + r];
     const uint4* s = reinterpret_cast<const uint4*>(src + (size_t)(slot / a_div) * lds);
     uint4* d = reinterpret_cast<uint4*>(dst + (size_t)(first + r) * ldd);
-    for (int c = lane; c < cols / 8; c += 32) d[c] = s[c];
+    const int n16 = cols / 8;
+    for (int c = lane; c < n16; c += 128) {
+      uint4 v[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (c + 32 * j < n16) v[j] = s[c + 32 * j];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (c + 32 * j < n16) d[c + 32 * j] = v[j];
+    }
   }
 }
 
@@ -313,7 +323,7 @@ MLXB_EXPORT int mlxb_moe_gather(const void* src, int lds, int a_div, const int* 
   if (max_tiles <= 0) return 0;
   if (cols <= 0 || (cols & 7) || (lds & 7) || (ldd & 7) || a_div <= 0 || (((uintptr_t)src | (uintptr_t)dst) & 15))
     return mlxb_fail(MLXB_BAD_ARG, "moe_gather: rows of %d columns at strides %d -> %d are not in whole 16 bytes", cols, lds, ldd);
-  launch_pdl(moe_gather_kernel, dim3(max_tiles), dim3(256), 0, stream, (const __nv_bfloat16*)src, lds, a_div, sorted,
+  launch_pdl(moe_gather_kernel, dim3(max_tiles, 16), dim3(256), 0, stream, (const __nv_bfloat16*)src, lds, a_div, sorted,
              tile_info, n_tiles, cols, (__nv_bfloat16*)dst, ldd);
   return mlxb_check_launch("moe_gather");
 }

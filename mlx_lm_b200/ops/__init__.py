@@ -49,7 +49,7 @@ _DT = {torch.float32: F32, torch.bfloat16: BF16}
 
 # kernel sources that only a bfloat16 run launches from: a float32 run neither compiles nor loads them
 BF16_ONLY_LIBS = frozenset({"gemm_smallm", "gemm_smallm_fold", "gemm_tcgen05", "attention_prefill",
-                            "attention_prefill_tc", "attention_wide_tc"})
+                            "attention_prefill_tc", "attention_wide_tc", "moe_tcgen05"})
 
 # status word bits set by kernels (csrc/common.cuh)
 ST_TOKEN_RANGE, ST_POSITION_RANGE, ST_PAGE_RANGE, ST_WAIT_TIMEOUT = 1, 2, 4, 8
@@ -525,7 +525,7 @@ PREFILL_TILE = int(_os.environ.get("MLXB_PREFILL_TILE", "128"))   # queries per 
 PREFILL_TC = _os.environ.get("MLXB_PREFILL_TC", "1") != "0"         # heads of 64 in tiles of 128 on the tcgen05 kernel
 
 _PRE_TC_ARGS = [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p]
+                c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_float, c_void_p, c_int, c_void_p]
 
 
 def attention_portions_supported(dtype, head_dim: int, scale: float = 1.0) -> bool:
@@ -533,9 +533,22 @@ def attention_portions_supported(dtype, head_dim: int, scale: float = 1.0) -> bo
     return dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= 128 and scale > 0
 
 
+def attention_portions_tc_supported(q, out, k_pool, v_pool, tile_rows: int = 0) -> bool:
+    """Whether portions over these pools run on the tcgen05 kernel (``attention_portions``): bfloat16, key and value
+    heads of 64, tiles of 128 queries, pages that are a power of two from 8 to 128, rows in whole 16 bytes."""
+    page, Dh = k_pool.shape[2], k_pool.shape[3]
+    return (PREFILL_TC and k_pool.dtype == torch.bfloat16 and Dh == 64 and v_pool is not None and v_pool.shape[3] == 64
+            and (tile_rows or PREFILL_TILE) == 128 and 8 <= page <= 128 and page & (page - 1) == 0
+            and _rows(q, "attention q") % 8 == 0 and _rows(out, "attention out") % 8 == 0
+            and q.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0)
+
+
 def attention_portions(q, tiles, n_tiles: int, block_table, k_pool, v_pool, out, n_heads: int, scale: float,
-                       window: int, status, stream, tile_rows: int = 0, sinks=None, first_positions=None) -> None:
+                       window: int, status, stream, tile_rows: int = 0, sinks=None, first_positions=None,
+                       keep_first: int = 0, softcap: float = 0.0, gate=None) -> None:
     """Causal attention of prompt portions on tensor cores (bfloat16, csrc/attention_prefill.cu).
+    ``keep_first``, ``softcap``, ``gate`` (bfloat16 ``[T, n_heads * 64]``, a sigmoid gate per output column): options of
+    the tcgen05 kernel only (``attention_portions_tc_supported``).
 
     ``tiles``: int32 device tensor ``[n_tiles, 4]``: first token row of the tile, queries in it (1..64),
     block-table row of its request, position of its first query.  ``first_positions``: int32, per block-table
@@ -552,12 +565,19 @@ def attention_portions(q, tiles, n_tiles: int, block_table, k_pool, v_pool, out,
         raise KernelError(f"attention_portions: {tiles.numel()} integers for {n_tiles} tiles")
     tile_rows = tile_rows or PREFILL_TILE
     ldq, ldo = _rows(q, "attention q"), _rows(out, "attention out")
-    if (PREFILL_TC and Dh == 64 and tile_rows == 128 and 8 <= page <= 128 and page & (page - 1) == 0
-            and ldq % 8 == 0 and ldo % 8 == 0 and q.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0):
+    if gate is not None:
+        _need(gate, torch.bfloat16, "attention_portions gate")
+        if gate.shape[0] != q.shape[0] or gate.shape[1] != n_heads * Dh:
+            raise KernelError(f"attention_portions: gate {tuple(gate.shape)} for {n_heads} heads of {Dh}")
+    if attention_portions_tc_supported(q, out, k_pool, v_pool, tile_rows):
         _call("attention_prefill_tc", "mlxb_attention_prefill_tc", _PRE_TC_ARGS, _p(q), ldq, q.shape[0], _p(tiles),
               n_tiles, _p(block_table), block_table.shape[1], n_pages, page, n_heads, Hkv, Dh, window, scale,
-              _p(k_pool), _p(v_pool), _p(out), ldo, _p(status), _sinks(sinks, n_heads, "attention_portions"), stream)
+              _p(k_pool), _p(v_pool), _p(out), ldo, _p(status), _sinks(sinks, n_heads, "attention_portions"),
+              int(keep_first or 0), float(softcap or 0.0), _p(gate), _rows(gate, "attention gate") if gate is not None else 0,
+              stream)
         return
+    if keep_first or softcap or gate is not None:
+        raise KernelError("attention_portions: kept first positions, a cap and a gate are options of the tcgen05 kernel")
     _call("attention_prefill", "mlxb_attention_prefill", _PRE_ARGS, _p(q), _rows(q, "attention q"), _p(tiles), n_tiles,
           tile_rows, _p(block_table), block_table.shape[1], n_pages, page, n_heads, Hkv, Dh, window, scale, _p(k_pool),
           _p(v_pool), _p(out), _rows(out, "attention out"), _p(status),
@@ -1022,11 +1042,21 @@ def attention_wide_tiles(q, q_head_stride: int, tiles, n_tiles: int, tile_querie
 
 def attention_wide_step(ctx, q, q_head_stride: int, cache_k, cache_v, block_table, out, out_head_stride: int, n_heads: int,
                         key_dim: int, value_dim: int, scale: float, window: int = 0, chunk: int = 0, talk=None,
-                        gate=None, softcap: float = 0.0, keep_first: int = 0) -> None:
+                        gate=None, softcap: float = 0.0, keep_first: int = 0, q_rounded=None) -> None:
     """All of a step's rows through ``attention_wide``: on tensor cores where the sizes allow it (the portions' tiles
-    and the single-token rows are two launches), else on the CUDA cores (float32 runs, odd sizes)."""
+    and the single-token rows are two launches), else on the CUDA cores (float32 runs, odd sizes).  ``q_rounded``: the
+    same queries in the pages' dtype, ``[T, n_heads * key_dim]``; with them the portions of plain heads of 64 (no score
+    mix, no runs of positions, a gate per column or none) go to the tcgen05 kernel of ``attention_portions``."""
     if attention_wide_tc_supported(cache_k, cache_v, n_heads, key_dim, value_dim, talk is not None):
-        if ctx.n_portion and ctx.portion_tiles is not None:
+        if (ctx.n_portion and ctx.portion_tiles is not None and q_rounded is not None and talk is None and not chunk
+                and key_dim == 64 and value_dim == 64 and out_head_stride == 64 and scale > 0
+                and (gate is None or gate.shape[1] == n_heads * value_dim)
+                and (gate is None or (_rows(gate, "attention gate") % 8 == 0 and gate.data_ptr() % 16 == 0))
+                and out.dtype == cache_k.dtype and attention_portions_tc_supported(q_rounded, out, cache_k, cache_v)):
+            attention_portions(q_rounded, ctx.portion_tiles, ctx.n_portion_tiles, block_table, cache_k, cache_v, out,
+                               n_heads, scale, window, ctx.status, ctx.stream, keep_first=keep_first, softcap=softcap,
+                               gate=gate)
+        elif ctx.n_portion and ctx.portion_tiles is not None:
             attention_wide_tiles(q, q_head_stride, ctx.portion_tiles, ctx.n_portion_tiles, PREFILL_TILE, block_table,
                                  cache_k, cache_v, out, out_head_stride, n_heads, key_dim, value_dim, scale, ctx.status,
                                  ctx.stream, window=window, chunk=chunk, talk=talk, gate=gate, softcap=softcap,
@@ -1205,6 +1235,15 @@ def moe_tile_rows(tensor_cores: bool) -> int:
     """Slots a tile of the experts' products takes: of the tensor-core kernel, or of the one on the CUDA cores."""
     f, _ = _fn("moe", "mlxb_moe_tile_rows", [c_int])
     return int(f(int(bool(tensor_cores))))
+
+
+def moe_few_rows() -> int:
+    """Slots a tile takes in the experts' products for a step of a few tokens (bfloat16, a warp per output column)."""
+    f, _ = _fn("moe", "mlxb_moe_tile_rows", [c_int])
+    return int(f(2))
+
+
+MOE_FEW_MAX_INNER = 6144     # the widest row the kernel for few slots keeps in shared memory
 
 
 def moe_route(logits, token_req, top: int, sel_expert, sel_weight, stream, score: str = "sigmoid",

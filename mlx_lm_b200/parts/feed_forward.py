@@ -95,6 +95,7 @@ class ExpertsMLP(FeedForward):
     replayable = True
     kernel_libs = ("moe", "moe_tcgen05", "dyt")
     MANY_SLOTS = 512     # (token, choice) slots of a step from which the 128-row tiles pay
+    FEW_SLOTS_AN_EXPERT = 8   # up to so many slots an expert on average, the weights are streamed by a warp per column
 
     def __init__(self, name: str, width: int, inner: int, n_experts: int, top: int, score: str = "sigmoid",
                  renormalize: bool = False, scale_input: bool = True, router_name: str = "router",
@@ -140,9 +141,11 @@ class ExpertsMLP(FeedForward):
         ops.moe_route(logits, ctx.token_req, top, sel_e, sel_w, ctx.stream, score=self.score, renormalize=self.renormalize)
         tc = x.dtype == torch.bfloat16 and D % 8 == 0 and F_ % 8 == 0 and x.stride(0) % 8 == 0
         # many slots: tiles of 128 rows of one expert on the 5th-generation tensor cores, the rows gathered in the
-        # plan's order first; few slots (decoding): tiles of 64 through the sorted list, or the CUDA cores
+        # plan's order first; few slots an expert (decoding): tiles of 4, a warp per output column; between them tiles
+        # of 64 on mma.sync through the sorted list; float32 and odd sizes: the CUDA cores
         many = tc and S >= self.MANY_SLOTS
-        rows = ops.moe_tc05_tile_rows() if many else ops.moe_tile_rows(tc)
+        few = tc and not many and S <= self.FEW_SLOTS_AN_EXPERT * E and max(D, F_) <= ops.MOE_FEW_MAX_INNER
+        rows = ops.moe_tc05_tile_rows() if many else ops.moe_few_rows() if few else ops.moe_tile_rows(tc)
         max_tiles = ops.moe_max_tiles(S, E, rows)
         order = ctx.ws.flat("moe_sorted", S, torch.int32)
         tiles = ctx.ws.flat("moe_tiles", 3 * max_tiles + 1, torch.int32)

@@ -333,6 +333,9 @@ class TalkingHeadsAttention(Mixer):
         self.out = Linear(f"{name}.o", n_heads * vdim, width, bias=False, weight_suffix="", init=init)
         self.has_bias, self.bias_init = bias, bias_init
         self.talk = self.freq = None
+        if dim == 64 and vdim == 64 and not rot_dims and not talk and not chunk and not head_gate:
+            # plain heads of 64: prompt portions run on the tcgen05 kernel
+            self.kernel_libs = type(self).kernel_libs + ("attention_prefill_tc",)
 
     def children(self):
         return (self.proj, self.out)
@@ -388,9 +391,11 @@ class TalkingHeadsAttention(Mixer):
         if self.head_gate or self.column_gate:
             g_off = self.proj.offset(f"{self.name}.g")
             gate = proj[:, g_off:g_off + (H * self.vdim if self.column_gate else H)]
+        # without a rotation the product's own (rounded) query columns are the queries
+        q_rounded = proj[:, :H * self.dim] if not self.rot_dims and proj.dtype == cache.k.dtype else None
         ops.attention_wide_step(ctx, q, self.key_row, cache.k, cache.v, cache.block_table, o, self.vdim, H, self.dim,
                                 self.vdim, self.scale, window=self.window or 0, chunk=self.chunk or 0, talk=self.talk,
-                                gate=gate, softcap=self.softcap, keep_first=self.keep_first)
+                                gate=gate, softcap=self.softcap, keep_first=self.keep_first, q_rounded=q_rounded)
         return o
 
     def _prepare(self, ctx, proj, cache, q) -> None:

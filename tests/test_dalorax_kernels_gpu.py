@@ -269,41 +269,42 @@ def test_experts_products(act, T, D, F, E, top):
         sel_e[11] = -1                   # a row that pads the step
     sel_w = torch.rand(S) + 0.2
     tc = act == torch.bfloat16 and D % 8 == 0 and F % 8 == 0
-    rows = ops.moe_tile_rows(tc)
-    max_tiles = ops.moe_max_tiles(S, E, rows)
-    order = torch.full((S,), -1, dtype=torch.int32, device=DEV)
-    tiles = torch.full((3 * max_tiles + 1,), -1, dtype=torch.int32, device=DEV)
-    ops.moe_plan(sel_e.flatten().to(DEV), S, E, rows, order, tiles, tiles[3 * max_tiles:], stream())
-    n = int(tiles[3 * max_tiles].item())
-    info = tiles[:3 * n].cpu().view(n, 3)
-    flat = sel_e.flatten()
-    live = int((flat >= 0).sum())
-    seen = []
-    for e, first, cnt in info.tolist():
-        assert 0 < cnt <= rows
-        slots = order[first:first + cnt].cpu().tolist()
-        assert all(int(flat[s]) == e for s in slots)
-        seen += slots
-    assert sorted(seen) == [s for s in range(S) if flat[s] >= 0] and len(seen) == live
-    assert n <= max_tiles and n <= (live + rows - 1) // rows + E
-    xd, wi, wo = x.to(DEV), w_in.to(DEV), w_out.to(DEV)
-    h = torch.full((S, F), 7.0, dtype=act, device=DEV)
-    ops.moe_gemm(xd, top, wi, F, order, tiles, tiles[3 * max_tiles:], max_tiles, rows, h, stream(), sel_weight=sel_w.to(DEV),
-                 gated=True)
-    y = torch.full((S, D), 7.0, device=DEV)
-    ops.moe_gemm(h, 1, wo, D, order, tiles, tiles[3 * max_tiles:], max_tiles, rows, y, stream())
-    tol = 2e-5 if act == torch.float32 else 3e-2
-    for s in range(S):
-        e = int(flat[s])
-        if e < 0:
-            assert bool((y[s] == 7.0).all())
-            continue
-        xs = sel_w[s].double() * x[s // top].double()
-        g, u = w_in[e, :F].double() @ xs, w_in[e, F:].double() @ xs
-        hs = g / (1 + torch.exp(-g)) * u
-        assert float((h[s].double().cpu() - hs).abs().max()) < tol * max(1.0, float(hs.abs().max())), ("hidden", s)
-        want = w_out[e].double() @ h[s].double().cpu()
-        assert float((y[s].double().cpu() - want).abs().max()) < tol * max(1.0, float(want.abs().max())), ("out", s)
+    # tiles of 64 on tensor cores (or 16 on the CUDA cores), and the tiles of 4 of steps with few tokens
+    for rows in [ops.moe_tile_rows(tc)] + ([ops.moe_few_rows()] if tc else []):
+        max_tiles = ops.moe_max_tiles(S, E, rows)
+        order = torch.full((S,), -1, dtype=torch.int32, device=DEV)
+        tiles = torch.full((3 * max_tiles + 1,), -1, dtype=torch.int32, device=DEV)
+        ops.moe_plan(sel_e.flatten().to(DEV), S, E, rows, order, tiles, tiles[3 * max_tiles:], stream())
+        n = int(tiles[3 * max_tiles].item())
+        info = tiles[:3 * n].cpu().view(n, 3)
+        flat = sel_e.flatten()
+        live = int((flat >= 0).sum())
+        seen = []
+        for e, first, cnt in info.tolist():
+            assert 0 < cnt <= rows
+            slots = order[first:first + cnt].cpu().tolist()
+            assert all(int(flat[s]) == e for s in slots)
+            seen += slots
+        assert sorted(seen) == [s for s in range(S) if flat[s] >= 0] and len(seen) == live
+        assert n <= max_tiles and n <= (live + rows - 1) // rows + E
+        xd, wi, wo = x.to(DEV), w_in.to(DEV), w_out.to(DEV)
+        h = torch.full((S, F), 7.0, dtype=act, device=DEV)
+        ops.moe_gemm(xd, top, wi, F, order, tiles, tiles[3 * max_tiles:], max_tiles, rows, h, stream(), sel_weight=sel_w.to(DEV),
+                     gated=True)
+        y = torch.full((S, D), 7.0, device=DEV)
+        ops.moe_gemm(h, 1, wo, D, order, tiles, tiles[3 * max_tiles:], max_tiles, rows, y, stream())
+        tol = 2e-5 if act == torch.float32 else 3e-2
+        for s in range(S):
+            e = int(flat[s])
+            if e < 0:
+                assert bool((y[s] == 7.0).all())
+                continue
+            xs = sel_w[s].double() * x[s // top].double()
+            g, u = w_in[e, :F].double() @ xs, w_in[e, F:].double() @ xs
+            hs = g / (1 + torch.exp(-g)) * u
+            assert float((h[s].double().cpu() - hs).abs().max()) < tol * max(1.0, float(hs.abs().max())), ("hidden", s)
+            want = w_out[e].double() @ h[s].double().cpu()
+            assert float((y[s].double().cpu() - want).abs().max()) < tol * max(1.0, float(want.abs().max())), ("out", s)
 
 
 @pytest.mark.parametrize("T,D,F,E,top", [(300, 96, 128, 5, 3), (700, 128, 72, 16, 2), (5, 64, 64, 3, 2), (260, 200, 136, 7, 1),
@@ -360,3 +361,77 @@ def test_experts_products_on_tcgen05(T, D, F, E, top):
     for s in range(S):
         if flat[s] < 0:
             assert bool((y[s] == 7.0).all())
+
+
+@pytest.mark.parametrize("H,G,window,keep_first,softcap,gated", [
+    (4, 2, 100, 5, 25.0, True),        # kept positions in the first block, the window several blocks on
+    (4, 1, 100, 130, 10.0, True),      # kept positions over two blocks
+    (2, 2, 300, 300, 0.0, False),      # no cap, no gate; the kept blocks meet the window's
+    (8, 2, 40, 1, 3.0, True),
+    (4, 4, 0, 0, 7.0, True),           # every key visible
+    (4, 2, 64, 0, 50.0, False),        # a window without kept positions
+])
+def test_portions_of_plain_heads_on_tcgen05(H, G, window, keep_first, softcap, gated):
+    """The tcgen05 kernel for prompt portions with a cap, kept first positions and a gate per column: tiles of 128
+    queries of one request that begin at many positions (block borders, the window's and the kept positions' edges
+    inside a tile), one cut short, one empty; rounded queries, float32 scores and softmax."""
+    from mlx_lm_b200 import ops
+    torch.manual_seed(H + window + keep_first)
+    T, page, d = 700, 16, 64
+    act = torch.bfloat16
+    q = (torch.randn(T, H, d) * 2.0).to(act).float()
+    k = torch.randn(T, G, d).to(act).float()
+    v = torch.randn(T, G, d).to(act).float()
+    gt = torch.randn(T, H * d).to(act).float()
+    scale = 3.0 / math.sqrt(d)
+    see = plain.visible(T, window or T + 1, keep_first)
+    heads = []
+    for h in range(H):
+        s = (q[:, h].double() @ k[:, h // (H // G)].double().T) * scale
+        if softcap:
+            s = softcap * torch.tanh(s / softcap)
+        heads.append(torch.softmax(s.masked_fill(~see, -math.inf), dim=-1) @ v[:, h // (H // G)].double())
+    want = torch.stack(heads, dim=1)
+    if gated:
+        want = want * torch.sigmoid(gt.double()).view(T, H, d)
+    n_pages = (T + page - 1) // page
+    order = list(reversed(range(n_pages)))
+    # rows nobody wrote hold a finite number, as in the engine's pools: the kernel multiplies them by zero
+    kp = torch.nan_to_num(paged(k, G, d, page, act, n_pages + 1, order), nan=3.0)
+    vp = torch.nan_to_num(paged(v, G, d, page, act, n_pages + 1, order), nan=3.0)
+    row = list(order)
+    if window and window < 500:
+        # pages wholly behind the window of the step's first position and beyond the kept ones are not the request's
+        gone = [lp for lp in range(n_pages) if (lp + 1) * page <= 512 - window + 1 and lp * page >= keep_first]
+        for lp in gone:
+            row[lp] = -1
+    table = i32([order + [-1] * 3, row + [-1] * 3])
+    qd = q.view(T, H * d).to(act).to(DEV)
+    gate = gt.to(act).to(DEV) if gated else None
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    starts = [0, 128, 256, 384, 512, 640]
+    tiles = i32([[s0, min(128, T - s0), 0, s0] for s0 in starts] + [[0, 0, 0, 0]])
+    out = torch.full((T, H * d), 7.0, dtype=act, device=DEV)
+    assert ops.attention_portions_tc_supported(qd, out, kp, vp)
+    ops.attention_portions(qd, tiles, len(starts) + 1, table, kp, vp, out, H, scale, window, status, stream(),
+                           keep_first=keep_first, softcap=softcap, gate=gate)
+    assert int(status.item()) == 0
+    err = (out.double().cpu().view(T, H, d) - want).abs().amax(dim=(1, 2))
+    assert float(err.max()) < 2e-2, (float(err.max()), int(err.argmax()))
+    # the same request after the cache gave back the pages behind the window of position 512
+    out1 = torch.full((T, H * d), 7.0, dtype=act, device=DEV)
+    ops.attention_portions(qd, i32([[512, 128, 1, 512], [640, T - 640, 1, 640]]), 2, table, kp, vp, out1, H, scale, window,
+                           status, stream(), keep_first=keep_first, softcap=softcap, gate=gate)
+    assert int(status.item()) == 0
+    assert torch.equal(out1[512:], out[512:])
+    # tiles that begin anywhere: a portion that starts in the middle of a block, of the window, of the kept positions
+    for s0, n in ((keep_first + 1, 100), (window + 3, 128), (200, 1), (333, 77), (T - 2, 2)):
+        if s0 + n > T:
+            continue
+        out2 = torch.full((T, H * d), 7.0, dtype=act, device=DEV)
+        ops.attention_portions(qd, i32([[s0, n, 0, s0]]), 1, table, kp, vp, out2, H, scale, window, status, stream(),
+                               keep_first=keep_first, softcap=softcap, gate=gate)
+        got = out2.double().cpu().view(T, H, d)
+        assert float((got[s0:s0 + n] - want[s0:s0 + n]).abs().max()) < 2e-2, (s0, n)
+        assert bool((out2[:s0] == 7.0).all()) and bool((out2[s0 + n:] == 7.0).all())
+    assert int(status.item()) == 0
