@@ -114,6 +114,12 @@ def sharpen(w, factor):
             w[k] *= factor
 
 
+def quiet_embedding(w, factor=0.04):
+    """The embedding scaled down (but for the routers' code columns), so that the layers and not the last token's own
+    row decide the next token: greedy generation then wanders instead of repeating itself."""
+    w["embed"][:, CODE_COLUMNS:] *= factor
+
+
 def with_mask(config, layer, **mask):
     c = copy.deepcopy(config)
     c["layers"][layer]["mixer"]["mask"].update(mask)

@@ -309,12 +309,14 @@ def test_experts_products(act, T, D, F, E, top):
 
 @pytest.mark.parametrize("T,D,F,E,top", [(300, 96, 128, 5, 3), (700, 128, 72, 16, 2), (5, 64, 64, 3, 2), (260, 200, 136, 7, 1),
                                           (1024, 256, 192, 4, 2), (40, 64, 8, 30, 4)])
-def test_experts_products_on_tcgen05(T, D, F, E, top):
+@pytest.mark.parametrize("tile_width", [128, 256])
+def test_experts_products_on_tcgen05(T, D, F, E, top, tile_width, monkeypatch):
     """Tiles of 128 slots of one expert: the rows gathered in the plan's order, the gated product's result in that
     order too, the second product's rows back at the slots' own places.  Inner sizes that are no multiple of the
     64-column stages or of the 64 / 128 output columns a CTA makes, experts without a slot, one expert with many
-    tiles, a row that pads the step."""
+    tiles, a row that pads the step; tiles that take 128 and 256 rows of the weights."""
     from mlx_lm_b200 import ops
+    monkeypatch.setenv("MLXB_MOE_BN", str(tile_width))
     torch.manual_seed(T + D + F + E)
     S = T * top
     act = torch.bfloat16
