@@ -4,16 +4,18 @@
 //                 the rows of one expert lie together and a tile of them is one TMA copy.
 // moe_gemm_tc05   per tile of the plan (up to 128 slots of one expert, rows first .. first + slots - 1 of the gathered
 //                 matrix) and block of output columns: out = A . W[expert]^T.  bfloat16 operands, float32 accumulation.
-//                 GATED: W holds [gate | up] rows; a CTA takes 64 gate rows and the 64 up rows of the same columns as
-//                 one 128-wide operand, and the epilogue writes silu(w g) * (w u) (w: the slot's routing weight, applied
-//                 to the float32 sums) as bfloat16 rows IN THE PLAN'S ORDER, ready to be the second product's operand.
-//                 Not gated: 128 output columns a CTA, float32 rows written to the slot's own row (out[sorted[i]]).
+//                 A tile takes BN = 128 or 256 rows of W (chosen on the host by what the rounds of tiles over the SMs
+//                 cost).  GATED: W holds [gate | up] rows; a CTA takes BN / 2 gate rows and the up rows of the same
+//                 columns as one BN-wide operand, and the epilogue writes silu(w g) * (w u) (w: the slot's routing
+//                 weight, applied to the float32 sums) as bfloat16 rows IN THE PLAN'S ORDER, ready to be the second
+//                 product's operand.  Not gated: BN output columns a CTA, float32 rows written to the slot's own row
+//                 (out[sorted[i]]).
 //
 // The kernel is persistent (one CTA per SM walks over the (tile, column block) pairs; how many tiles there are is read
 // from the plan on the device) and has the roles of the linear kernel in gemm_tcgen05.cu: warp 0 is the TMA producer
-// (a ring of stages of 128 x 64 tiles of A and two 64 x 64 tiles of W, 128-byte swizzle), warp 1 owns the tensor
-// memory and issues tcgen05.mma into one of two 128 x 128 float32 accumulators, warps 2-9 are the epilogue (two per
-// quadrant of TMEM lanes).  Rows of a tile beyond the expert's slots hold another expert's rows or zeros; they are
+// (a ring of stages of a 128 x 64 tile of A and BN / 64 boxes of 64 x 64 of W, 128-byte swizzle), warp 1 owns the
+// tensor memory and issues tcgen05.mma into one of two 128 x BN float32 accumulators, warps 2-9 are the epilogue (two
+// per quadrant of TMEM lanes).  Rows of a tile beyond the expert's slots hold another expert's rows or zeros; they are
 // computed and not stored.  Every wait on an mbarrier is bounded; a timeout raises MLXB_ST_WAIT_TIMEOUT and all roles
 // leave through the common exit, where the tensor memory is freed.
 // A slot's result does not depend on which tile it lands in or on its place there: the sum over K runs stage by
@@ -22,17 +24,19 @@
 
 MLXB_DEFINE_LAST_ERROR()
 
-constexpr int MT_BM = 128, MT_BK = 64, MT_BN = 128, MT_STAGES = 6;
+constexpr int MT_BM = 128, MT_BK = 64;
 constexpr int MT_EPI_WARPS = 8;
 constexpr int MT_THREADS = 64 + 32 * MT_EPI_WARPS;
-constexpr uint32_t MT_STAGE_BYTES = (MT_BM + MT_BN) * MT_BK * sizeof(__nv_bfloat16);
-constexpr uint32_t MT_TMEM_COLS = 256;   // two accumulators of 128 columns
+// BN: rows of W a tile takes (128 or 256); a wider tile moves fewer bytes a flop, a narrower one leaves fewer SMs idle
+// in the last round of a small problem.
+constexpr int mt_stages(int bn) { return bn == 256 ? 4 : 6; }
 
+template <int BN>
 struct MoeSmem {
-  alignas(1024) __nv_bfloat16 a[MT_STAGES][MT_BM * MT_BK];
-  alignas(1024) __nv_bfloat16 b[MT_STAGES][MT_BN * MT_BK];
-  alignas(8) uint64_t full[MT_STAGES];
-  uint64_t empty[MT_STAGES];
+  alignas(1024) __nv_bfloat16 a[mt_stages(BN)][MT_BM * MT_BK];
+  alignas(1024) __nv_bfloat16 b[mt_stages(BN)][BN * MT_BK];
+  alignas(8) uint64_t full[mt_stages(BN)];
+  uint64_t empty[mt_stages(BN)];
   uint64_t acc_full[2];
   uint64_t acc_empty[2];
   uint64_t drained;
@@ -72,13 +76,16 @@ __global__ void moe_gather_kernel(const __nv_bfloat16* src, int lds, int a_div, 
   }
 }
 
-template <bool GATED>
+template <bool GATED, int BN>
 __global__ void __launch_bounds__(MT_THREADS)
 moe_gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                      const int* sorted, const int* tile_info, const int* n_tiles_p, int NW, int N, int K,
                      const float* sel_weight, void* out_v, int ldo, int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
-  MoeSmem& sm = *reinterpret_cast<MoeSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  MoeSmem<BN>& sm = *reinterpret_cast<MoeSmem<BN>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  constexpr int MT_BN = BN, MT_STAGES = mt_stages(BN), HALF = BN / 2;
+  constexpr uint32_t MT_STAGE_BYTES = (MT_BM + BN) * MT_BK * sizeof(__nv_bfloat16);
+  constexpr uint32_t MT_TMEM_COLS = 2 * BN;   // two accumulators
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int k_tiles = (K + MT_BK - 1) / MT_BK;
   constexpr int COLS = GATED ? MT_BN / 2 : MT_BN;        // output columns a CTA's tile makes
@@ -119,16 +126,19 @@ moe_gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
         const int t = w % n_tiles, nb = w / n_tiles;
         const int expert = tile_info[3 * t], first = tile_info[3 * t + 1];
-        const int w0 = expert * NW + nb * COLS;                    // gate rows, or the first 64 output rows
-        const int w1 = GATED ? w0 + NW / 2 : w0 + MT_BN / 2;       // up rows of the same columns, or the next 64
+        const int w0 = expert * NW + nb * COLS;                    // gate rows, or the first half of the output rows
+        const int w1 = GATED ? w0 + NW / 2 : w0 + HALF;            // up rows of the same columns, or the second half
         for (int kt = 0; kt < k_tiles; ++kt, ++issued) {
           const int s = issued % MT_STAGES;
           const uint32_t ph = (issued / MT_STAGES) & 1;
           if (issued >= MT_STAGES && !mbar_wait(&sm.empty[s], ph ^ 1, abort_flag)) { ok = false; break; }
           mbar_expect_tx(&sm.full[s], MT_STAGE_BYTES);
           tma_load_2d(sm.a[s], &map_a, kt * MT_BK, first, &sm.full[s]);
-          tma_load_2d(sm.b[s], &map_w, kt * MT_BK, w0, &sm.full[s]);
-          tma_load_2d(sm.b[s] + (MT_BN / 2) * MT_BK, &map_w, kt * MT_BK, w1, &sm.full[s]);
+#pragma unroll
+          for (int i = 0; i < HALF / 64; ++i) {   // boxes of 64 rows: in the 128-byte swizzle simply consecutive 8-row groups
+            tma_load_2d(sm.b[s] + (64 * i) * MT_BK, &map_w, kt * MT_BK, w0 + 64 * i, &sm.full[s]);
+            tma_load_2d(sm.b[s] + (HALF + 64 * i) * MT_BK, &map_w, kt * MT_BK, w1 + 64 * i, &sm.full[s]);
+          }
         }
       }
       if (*abort_flag) {   // gave up: let the copies already issued land before the CTA exits
@@ -187,24 +197,29 @@ moe_gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * MT_BN);
       if (GATED) {
-        uint32_t g[32], u[32];
-        tmem_ld32(taddr + (uint32_t)(32 * half), g);
-        tmem_ld32(taddr + (uint32_t)(MT_BN / 2 + 32 * half), u);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        mbar_arrive(&sm.acc_empty[b]);
-        if (live) {
-          __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out_v) + (size_t)(first + r) * ldo;
-          const int n0 = nb * COLS + 32 * half;
+        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out_v) + (size_t)(first + r) * ldo;
+#pragma unroll 1
+        for (int c0 = 0; c0 < HALF / 2; c0 += 32) {   // this warp's output columns: gate and up of a column in one lane
+          uint32_t g[32], u[32];
+          tmem_ld32(taddr + (uint32_t)(HALF / 2 * half + c0), g);
+          tmem_ld32(taddr + (uint32_t)(HALF + HALF / 2 * half + c0), u);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          if (c0 + 32 >= HALF / 2) {
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive(&sm.acc_empty[b]);
+          }
+          if (live) {
+            const int n0 = nb * COLS + HALF / 2 * half + c0;
 #pragma unroll
-          for (int g8 = 0; g8 < 4; ++g8) {
-            const int n8 = n0 + 8 * g8;
-            if (n8 >= N) break;                 // N is a multiple of 8: a group is whole or absent
-            float v[8];
+            for (int g8 = 0; g8 < 4; ++g8) {
+              const int n8 = n0 + 8 * g8;
+              if (n8 >= N) break;                 // N is a multiple of 8: a group is whole or absent
+              float v[8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i)
-              v[i] = mt_silu(wgt * __uint_as_float(g[8 * g8 + i])) * (wgt * __uint_as_float(u[8 * g8 + i]));
-            *reinterpret_cast<uint4*>(o + n8) = pack8(v);
+              for (int i = 0; i < 8; ++i)
+                v[i] = mt_silu(wgt * __uint_as_float(g[8 * g8 + i])) * (wgt * __uint_as_float(u[8 * g8 + i]));
+              *reinterpret_cast<uint4*>(o + n8) = pack8(v);
+            }
           }
         }
       } else {
@@ -295,22 +310,26 @@ struct MtLaunch {
   void* out;
   int ldo;
   int* status;
-  dim3 grid;
-  size_t smem;
+  int max_tiles;
   cudaStream_t stream;
 };
 
-template <bool GATED>
+template <bool GATED, int BN>
 static int mt_launch(const MtLaunch& l) {
-  auto kern = moe_gemm_tc05_kernel<GATED>;
+  static_assert(sizeof(MoeSmem<BN>) + 1024 <= 227 * 1024, "the stages fit a CTA's shared memory");
+  auto kern = moe_gemm_tc05_kernel<GATED, BN>;
+  const size_t smem = sizeof(MoeSmem<BN>) + 1024;
   static bool raised = false;   // once per kernel, and never for the first time inside a stream capture
   if (!raised) {
-    cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)l.smem);
+    cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (err != cudaSuccess)
-      return mlxb_fail((int)err, "moe_gemm (tensor cores): %zu bytes of shared memory: %s", l.smem, cudaGetErrorString(err));
+      return mlxb_fail((int)err, "moe_gemm (tensor cores): %zu bytes of shared memory: %s", smem, cudaGetErrorString(err));
     raised = true;
   }
-  launch_pdl(kern, l.grid, dim3(MT_THREADS), l.smem, l.stream, l.ma, l.mw, l.sorted, l.tile_info, l.n_tiles, l.NW, l.N, l.K,
+  const int cols = GATED ? BN / 2 : BN;
+  const long long work = (long long)l.max_tiles * ((l.N + cols - 1) / cols);
+  const dim3 grid((unsigned)(work < mt_sm_count() ? work : mt_sm_count()));
+  launch_pdl(kern, grid, dim3(MT_THREADS), smem, l.stream, l.ma, l.mw, l.sorted, l.tile_info, l.n_tiles, l.NW, l.N, l.K,
              l.sel_weight, l.out, l.ldo, l.status);
   return mlxb_check_launch("moe_gemm (tensor cores)");
 }
@@ -328,6 +347,26 @@ MLXB_EXPORT int mlxb_moe_gather(const void* src, int lds, int a_div, const int* 
   return mlxb_check_launch("moe_gather");
 }
 
+// How many rows of W a tile takes: the width whose rounds of tiles over the SMs cost least, a tile's cost being the
+// rows it streams per K step (128 of A plus BN of W).  How many tiles the plan holds is known on the device only: the
+// estimate is full tiles plus half a tile an expert.  The second product stays at 128: its epilogue writes float32 rows,
+// four times the bytes a column of the gated product's, and with 256 columns a tile the two accumulators no longer
+// hide it (measured: 24.6 against 20.1 us at width 1024, 43.8 against 41.0 at width 2048).
+static int mt_tile_width(int S, int E, int N, bool gated) {
+  if (const char* force = getenv("MLXB_MOE_BN")) return atoi(force) == 256 ? 256 : 128;   // experiments and tests
+  if (!gated) return 128;
+  const long long tiles = (S + MT_BM - 1) / MT_BM + (E + 1) / 2;
+  int best = 128;
+  long long best_cost = -1;
+  for (int bn : {256, 128}) {
+    const int cols = gated ? bn / 2 : bn;
+    const long long work = tiles * ((N + cols - 1) / cols);
+    const long long cost = ((work + mt_sm_count() - 1) / mt_sm_count()) * (MT_BM + bn);
+    if (best_cost < 0 || cost < best_cost) { best = bn; best_cost = cost; }
+  }
+  return best;
+}
+
 // A: bfloat16 [S, lda], rows in the plan's order; W: bfloat16 [E][NW][K] contiguous, NW = 2 N (gated: gate rows, then up
 // rows) or N.  gated: out bfloat16 [S, ldo] in the plan's order = silu(w g) * (w u); else out float32 [S, ldo], row
 // sorted[i] = the product of row i.  The plan was made with tiles of mlxb_moe_tc05_tile_rows() slots.
@@ -340,14 +379,10 @@ MLXB_EXPORT int mlxb_moe_gemm_tc05(int gated, const void* A, int lda, int S, con
       NW != (gated ? 2 : 1) * N || (gated && !sel_weight) || (((uintptr_t)A | (uintptr_t)W | (uintptr_t)out) & 15) ||
       (long long)E * NW > 0x7fffffffLL)
     return mlxb_fail(MLXB_BAD_ARG, "moe_gemm (tensor cores): %d experts of %d x %d, strides %d / %d", E, NW, K, lda, ldo);
-  CUtensorMap ma, mw;
-  if (int e = mt_make_map(&ma, A, S, K, lda, MT_BM)) return e;
-  if (int e = mt_make_map(&mw, W, (long long)E * NW, K, K, MT_BN / 2)) return e;
-  const size_t smem = sizeof(MoeSmem) + 1024;
-  static_assert(sizeof(MoeSmem) + 1024 <= 227 * 1024, "the stages fit a CTA's shared memory");
-  const int n_blocks = (N + (gated ? MT_BN / 2 : MT_BN) - 1) / (gated ? MT_BN / 2 : MT_BN);
-  const long long work = (long long)max_tiles * n_blocks;
-  const dim3 grid((unsigned)(work < mt_sm_count() ? work : mt_sm_count()));
-  const MtLaunch l = {ma, mw, sorted, tile_info, n_tiles, NW, N, K, sel_weight, out, ldo, status, grid, smem, stream};
-  return gated ? mt_launch<true>(l) : mt_launch<false>(l);
+  MtLaunch l = {{}, {}, sorted, tile_info, n_tiles, NW, N, K, sel_weight, out, ldo, status, max_tiles, stream};
+  if (int e = mt_make_map(&l.ma, A, S, K, lda, MT_BM)) return e;
+  if (int e = mt_make_map(&l.mw, W, (long long)E * NW, K, K, 64)) return e;
+  const int bn = mt_tile_width(S, E, N, gated != 0);
+  if (bn == 256) return gated ? mt_launch<true, 256>(l) : mt_launch<false, 256>(l);
+  return gated ? mt_launch<true, 128>(l) : mt_launch<false, 128>(l);
 }
