@@ -167,8 +167,8 @@ class CacheManager:
             if g.spec.value_dim == 0:
                 g.v = g.k        # values are read out of the key rows
             else:
-                g.v = torch.zeros(shape[:-1] + (g.spec.value_dim or g.spec.head_dim,), dtype=self.dtype,
-                                  device=self.device)
+                g.v = torch.zeros((shape[0], n_pages, g.spec.value_heads or g.spec.n_kv_heads, self.page_size,
+                                   g.spec.value_dim or g.spec.head_dim), dtype=self.dtype, device=self.device)
         for g in self.state_groups:
             shape = (len(g.cache_ids), self.max_requests) + tuple(g.spec.shape)
             g.data = torch.zeros(shape, dtype=torch.float32, device=self.device)

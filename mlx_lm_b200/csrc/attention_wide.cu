@@ -4,6 +4,8 @@
 //   * scores mixed across heads before the softmax ("talking heads"): s'_h = sum_g talk[h, g] s_g, where
 //     s_g = scale * q_g . k_kv(g) is head g's raw score for the same (query, key) pair.  All heads of the
 //     query must then be in one CTA (the group is all heads);
+//   * fewer value heads than key heads (Hv of them: key heads c * Hkv/Hv .. read value head c; several score maps
+//     over the same values);
 //   * keys and values of different widths, and values that are a prefix of the key row itself (v_pool may be
 //     k_pool: a cache of latent rows [c | rotated part] read as keys of width Dk and as values of width Dv);
 //   * the visible keys of position p given by a window (p - window < j <= p), by chunks counted from position
@@ -72,11 +74,12 @@ attention_wide_kernel(const float* q, int ldq, int qhs, const int* __restrict__ 
                       int n_pages, int page, int Hq, int Hkv, int HB, int Dk, int Dv, int krs, int vrs, int window,
                       int chunk, float scale, const float* __restrict__ talk, const T* k_pool, const T* v_pool,
                       const T* gate, int ldg, TO* __restrict__ out, int ldo, int ohs, const int* __restrict__ rows,
-                      int* __restrict__ status, float softcap, int keep_first, int gate_cols) {
+                      int* __restrict__ status, float softcap, int keep_first, int gate_cols, int Hv) {
   extern __shared__ __align__(16) unsigned char aw_smem[];
   const int DkP = (Dk + 3) & ~3;
   long long* sRow = reinterpret_cast<long long*>(aw_smem);   // [KB] row of the key in head 0 of its page, or -1
-  float* sq = reinterpret_cast<float*>(sRow + AW_KB);        // [HB][DkP]
+  long long* sRowV = sRow + AW_KB;                           // [KB] the same among the value heads
+  float* sq = reinterpret_cast<float*>(sRowV + AW_KB);       // [HB][DkP]
   float* sS = sq + HB * DkP;                                 // [HB][KB] raw scores
   float* sP = sS + HB * AW_KB;                               // [HB][KB] mixed scores, then weights
   float* sT = sP + HB * AW_KB;                               // [HB][HB] the mixing matrix
@@ -103,7 +106,7 @@ attention_wide_kernel(const float* q, int ldq, int qhs, const int* __restrict__ 
     sq[e] = d < Dk ? q[(size_t)t * ldq + (size_t)(h0 + hh) * qhs + d] : 0.f;
   }
   const int* bt = block_table + (size_t)r * max_pages;
-  const int rep = Hq / Hkv;
+  const int rep = Hq / Hkv, vrep = rep * (Hkv / Hv);       // query heads a key head, and a value head, serves
   int lo = 0;
   if (window > 0 && p - window + 1 > lo) lo = p - window + 1;
   if (chunk > 0 && (p / chunk) * chunk > lo) lo = (p / chunk) * chunk;
@@ -126,15 +129,16 @@ attention_wide_kernel(const float* q, int ldq, int qhs, const int* __restrict__ 
     const int nk = min(AW_KB, j_end - j0 + 1);
     __syncthreads();        // the block before is done with sRow and sP (first pass: sq, sM are written)
     if (tid < AW_KB) {
-      long long row = -1;
+      long long row = -1, vrow = -1;
       if (tid < nk) {
         const int j = j0 + tid, lp = j / page;
         const int pg = lp < max_pages ? bt[lp] : -1;
         if (pg >= n_pages) atomicOr(status, MLXB_ST_PAGE_RANGE);
         else if (pg < 0) atomicOr(status, MLXB_ST_POSITION_RANGE);   // a key inside the range has no page
-        else row = (long long)pg * Hkv * page + (j % page);
+        else { row = (long long)pg * Hkv * page + (j % page); vrow = (long long)pg * Hv * page + (j % page); }
       }
       sRow[tid] = row;
+      sRowV[tid] = vrow;
     }
     __syncthreads();
     // A: raw scores
@@ -211,14 +215,14 @@ attention_wide_kernel(const float* q, int ldq, int qhs, const int* __restrict__ 
       }
     }
     for (int jj = 0; jj < nk; ++jj) {
-      const long long row = sRow[jj];
+      const long long row = sRowV[jj];
       if (row < 0) continue;
 #pragma unroll
       for (int i = 0; i < AW_MAXO; ++i) {
         if (tid + i * AW_THREADS < n_items) {
           const int hh = item_h[i];
           const float w = sP[hh * AW_KB + jj];
-          const T* vp = v_pool + (size_t)(row + (long long)((h0 + hh) / rep) * page) * vrs + item_d[i];
+          const T* vp = v_pool + (size_t)(row + (long long)((h0 + hh) / vrep) * page) * vrs + item_d[i];
           if (VECV) {
             float a, b;
             load2<T>(vp, a, b);
@@ -262,7 +266,7 @@ static int aw_launch(const float* q, int ldq, int qhs, const int* positions, con
                      const int* block_table, int max_pages, int n_pages, int page, int Hq, int Hkv, int HB, int Dk,
                      int Dv, int krs, int vrs, int window, int chunk, float scale, const float* talk,
                      const void* k_pool, const void* v_pool, const void* gate, int ldg, void* out, int ldo, int ohs,
-                     const int* rows, int n_tokens, int* status, float softcap, int keep_first, int gate_cols,
+                     const int* rows, int n_tokens, int* status, float softcap, int keep_first, int gate_cols, int Hv,
                      cudaStream_t stream) {
   constexpr int NK = KVec<T>::N;
   const bool veck = Dk % NK == 0 && krs % NK == 0 && ((uintptr_t)k_pool & 15) == 0;
@@ -271,7 +275,7 @@ static int aw_launch(const float* q, int ldq, int qhs, const int* positions, con
   if (items > AW_MAXO * AW_THREADS)
     return mlxb_fail(MLXB_BAD_ARG, "attention (wide): %d heads of %d value columns are more than a CTA takes", HB, Dv);
   const int DkP = (Dk + 3) & ~3;
-  const size_t smem = sizeof(long long) * AW_KB +
+  const size_t smem = sizeof(long long) * 2 * AW_KB +
                       sizeof(float) * ((size_t)HB * DkP + 2 * (size_t)HB * AW_KB + (size_t)HB * HB + 3 * (size_t)HB);
   const dim3 grid(n_tokens, Hq / HB), block(AW_THREADS);
 #define AW_GO(VK, VV)                                                                                                  \
@@ -284,7 +288,7 @@ static int aw_launch(const float* q, int ldq, int qhs, const int* positions, con
     }                                                                                                                  \
     launch_pdl(kern, grid, block, smem, stream, q, ldq, qhs, positions, token_req, block_table, max_pages, n_pages,    \
                page, Hq, Hkv, HB, Dk, Dv, krs, vrs, window, chunk, scale, talk, (const T*)k_pool, (const T*)v_pool,    \
-               (const T*)gate, ldg, (TO*)out, ldo, ohs, rows, status, softcap, keep_first, gate_cols);                 \
+               (const T*)gate, ldg, (TO*)out, ldo, ohs, rows, status, softcap, keep_first, gate_cols, Hv);                 \
   } while (0)
   if (veck && vecv) AW_GO(true, true);
   else if (veck) AW_GO(true, false);
@@ -298,15 +302,17 @@ static int aw_launch(const float* q, int ldq, int qhs, const int* positions, con
 // [Hq, Hq] or null; gate: `dtype` [*, ldg] (one column per head) or null; out: `dtype`, or float32 if out_f32, head h
 // from column h*ohs, Dv values; rows: int32 [n_tokens] token rows to take, or null for 0..n_tokens-1;
 // window, chunk <= 0: none; softcap <= 0: none; keep_first: positions 0 .. keep_first-1 stay visible beside the window;
-// gate_cols: gate has Hq * Dv columns, one per output column.
+// gate_cols: gate has Hq * Dv columns, one per output column.  Hv: heads of v_pool (0: Hkv).
 MLXB_EXPORT int mlxb_attention_wide(int dtype, int out_f32, const float* q, int ldq, int qhs, const int* positions,
                                     const int* token_req, const int* block_table, int max_pages, int n_pages, int page,
                                     int Hq, int Hkv, int Dk, int Dv, int krs, int vrs, int window, int chunk,
                                     float scale, const float* talk, const void* k_pool, const void* v_pool,
                                     const void* gate, int ldg, void* out, int ldo, int ohs, const int* rows,
-                                    int n_tokens, int* status, float softcap, int keep_first, int gate_cols,
+                                    int n_tokens, int* status, float softcap, int keep_first, int gate_cols, int Hv,
                                     cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
+  if (Hv <= 0) Hv = Hkv;
+  if (Hkv % Hv) return mlxb_fail(MLXB_BAD_ARG, "attention (wide): %d key heads over %d value heads", Hkv, Hv);
   if (page <= 0 || (page & (page - 1)) || Hq <= 0 || Hkv <= 0 || Hq % Hkv || Dk <= 0 || Dv <= 0 || krs < Dk || vrs < Dv ||
       qhs < Dk || ohs < Dv)
     return mlxb_fail(MLXB_BAD_ARG, "attention (wide): %d/%d heads, sizes %d/%d in rows of %d/%d, page %d", Hq, Hkv, Dk,
@@ -321,14 +327,14 @@ MLXB_EXPORT int mlxb_attention_wide(int dtype, int out_f32, const float* q, int 
   if (dtype == MLXB_F32)
     return aw_launch<float, float>(q, ldq, qhs, positions, token_req, block_table, max_pages, n_pages, page, Hq, Hkv, HB,
                                    Dk, Dv, krs, vrs, window, chunk, scale, talk, k_pool, v_pool, gate, ldg, out, ldo, ohs,
-                                   rows, n_tokens, status, softcap, keep_first, gate_cols, stream);
+                                   rows, n_tokens, status, softcap, keep_first, gate_cols, Hv, stream);
   if (dtype == MLXB_BF16 && out_f32)
     return aw_launch<__nv_bfloat16, float>(q, ldq, qhs, positions, token_req, block_table, max_pages, n_pages, page, Hq,
                                            Hkv, HB, Dk, Dv, krs, vrs, window, chunk, scale, talk, k_pool, v_pool, gate,
-                                           ldg, out, ldo, ohs, rows, n_tokens, status, softcap, keep_first, gate_cols, stream);
+                                           ldg, out, ldo, ohs, rows, n_tokens, status, softcap, keep_first, gate_cols, Hv, stream);
   if (dtype == MLXB_BF16)
     return aw_launch<__nv_bfloat16, __nv_bfloat16>(q, ldq, qhs, positions, token_req, block_table, max_pages, n_pages,
                                                    page, Hq, Hkv, HB, Dk, Dv, krs, vrs, window, chunk, scale, talk, k_pool,
-                                                   v_pool, gate, ldg, out, ldo, ohs, rows, n_tokens, status, softcap, keep_first, gate_cols, stream);
+                                                   v_pool, gate, ldg, out, ldo, ohs, rows, n_tokens, status, softcap, keep_first, gate_cols, Hv, stream);
   return mlxb_fail(MLXB_BAD_DTYPE, "attention (wide): dtype code %d", dtype);
 }

@@ -61,7 +61,7 @@ attention_wide_tc_kernel(const float* q, int ldq, int qhs, const int* __restrict
                          int chunk, float scale, const float* __restrict__ talk, const __nv_bfloat16* k_pool,
                          const __nv_bfloat16* v_pool, const __nv_bfloat16* gate, int ldg, TO* __restrict__ out, int ldo,
                          int ohs, int* __restrict__ status, int bps, int n_rel, float* __restrict__ scratch, int nbuf,
-                         float softcap, int keep_first, int gate_cols) {
+                         float softcap, int keep_first, int gate_cols, int Hv) {
   constexpr int M = TC_M * MP, THREADS = TC_THREADS * MP;
   extern __shared__ __align__(16) unsigned char tc_smem[];
   const int ldk = DkE + 8, ldv = shared_v ? ldk : Dv + 8;
@@ -146,7 +146,7 @@ attention_wide_tc_kernel(const float* q, int ldq, int qhs, const int* __restrict
         if ((j >= lo_min || j < keep_first) && j <= p_max) {
           const int lp = j / page;
           const int pg = lp < max_pages ? bt[lp] : -1;
-          if (pg >= 0 && pg < n_pages) src = v_pool + (((size_t)pg * Hkv + cv) * page + (j % page)) * vrs + col;
+          if (pg >= 0 && pg < n_pages) src = v_pool + (((size_t)pg * Hv + cv / (Hkv / Hv)) * page + (j % page)) * vrs + col;
         }
         if (src) cp_async16(dV + jj * ldv + col, src);
         else *reinterpret_cast<uint4*>(dV + jj * ldv + col) = make_uint4(0u, 0u, 0u, 0u);
@@ -478,14 +478,18 @@ MLXB_EXPORT int mlxb_attention_wide_tc_supported(int Hq, int Hkv, int Dk, int Dv
 }
 
 // The arguments of mlxb_attention_wide with bfloat16 pools, and instead of the token rows a list of tiles: int32
-// [n_tiles, 4] = (first token row, queries, block-table row, first position), each of at most tile_q queries.
+// [n_tiles, 4] = (first token row, queries, block-table row, first position), each of at most tile_q queries.  Hv: heads
+// of v_pool (0: Hkv); with fewer, key heads c * Hkv/Hv .. read value head c.
 MLXB_EXPORT int mlxb_attention_wide_tc(int out_f32, const float* q, int ldq, int qhs, const int* tiles, int n_tiles,
                                        int tile_q, const int* block_table, int max_pages, int n_pages, int page, int Hq,
                                        int Hkv, int Dk, int Dv, int krs, int vrs, int window, int chunk, float scale,
                                        const float* talk, const void* k_pool, const void* v_pool, const void* gate,
                                        int ldg, void* out, int ldo, int ohs, int* status, float* scratch, int max_len,
-                                       float softcap, int keep_first, int gate_cols, cudaStream_t stream) {
+                                       float softcap, int keep_first, int gate_cols, int Hv, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
+  if (Hv <= 0) Hv = Hkv;
+  if (Hkv % Hv || (Hv != Hkv && v_pool == k_pool))
+    return mlxb_fail(MLXB_BAD_ARG, "attention (wide, tensor cores): %d key heads over %d value heads", Hkv, Hv);
   TcPlan pl;
   const int shared_v = v_pool == k_pool;
   if (!tc_plan(Hq, Hkv, Dk, Dv, krs, vrs, talk != nullptr, shared_v, tile_q > 1, &pl) || page <= 0 || (page & (page - 1)) ||
@@ -515,7 +519,7 @@ MLXB_EXPORT int mlxb_attention_wide_tc(int out_f32, const float* q, int ldq, int
     launch_pdl(kern, grid, block, (size_t)smem, stream, q, ldq, qhs, tiles, subs, TQ, pl.HG, block_table, max_pages,   \
                n_pages, page, Hq, Hkv, Dk, Dv, pl.DkE, pl.seg, pl.n_seg, krs, vrs, shared_v, window, chunk, scale, talk, \
                (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, (const __nv_bfloat16*)gate, ldg, (TO*)out,  \
-               ldo, ohs, status, bps, n_rel, scratch, pl.nbuf, softcap, keep_first, gate_cols);                        \
+               ldo, ohs, status, bps, n_rel, scratch, pl.nbuf, softcap, keep_first, gate_cols, Hv);                        \
     if (split) {                                                                                                       \
       if (int e = mlxb_check_launch("attention (wide, tensor cores)")) return e;                                       \
       launch_pdl(attention_wide_merge_kernel<TO>, dim3(n_tiles, Hq), dim3(Dv >= 128 ? 128 : 64), 0, stream, tiles, Hq, \

@@ -1,18 +1,20 @@
 // Small row-wise kernels between the products of a layer.
-//   gated_unit      out[t, j] = act(in[t, j]) * in[t, F + j]: the two halves of a fused [gate | up] projection
-//                   (act: silu = z * sigmoid(z)); float32 arithmetic, rounded once.
+//   gated_unit      out[t, j] = unit(in[t, j], in[t, F + j]): the two halves of a fused [gate | up] projection through
+//                   the gated unit of kind `act` (gated_unit.cuh: silu(g) * u, or the bounded unit with `limit`);
+//                   float32 arithmetic, rounded once.
 //   scale_by_rows   out[t, j] = in[t, j] * table[index[t], first + j]: a per-token vector looked up in a table.
 //   xielu           out[t, j] = f(in[t, j]) with two learned numbers (a, b) of the layer, read from device memory:
 //                   z > 0: softplus(a) z^2 + z/2;  z <= 0: (1/2 + softplus(b)) (exp(z) - 1 - z) + z/2.  In place if out = in.
 //   join_rows       out[t] = [a[t] | b[t]] in the activation dtype from float32 rows (b may be null: a plain cast).
 #include "common.cuh"
+#include "gated_unit.cuh"
 
 MLXB_DEFINE_LAST_ERROR()
 
 __device__ __forceinline__ float silu_f(float v) { return v / (1.f + expf(-v)); }
 
 template <typename T>
-__global__ void gated_unit_kernel(const T* in, int ldi, T* __restrict__ out, int ldo, int F, int n) {
+__global__ void gated_unit_kernel(const T* in, int ldi, T* __restrict__ out, int ldo, int F, int n, int act, float limit) {
   pdl_wait();
   pdl_trigger();
   in = after_wait(in);
@@ -20,12 +22,12 @@ __global__ void gated_unit_kernel(const T* in, int ldi, T* __restrict__ out, int
   if (idx >= (long long)n * F) return;
   const int t = (int)(idx / F), j = (int)(idx - (long long)t * F);
   const T* row = in + (size_t)t * ldi;
-  out[(size_t)t * ldo + j] = from_f<T>(silu_f(to_f(row[j])) * to_f(row[F + j]));
+  out[(size_t)t * ldo + j] = from_f<T>(mlxb_gated_unit(act, to_f(row[j]), to_f(row[F + j]), 1.f, limit));
 }
 
 // Eight elements a thread (bfloat16 rows whose halves, strides and bases allow 16-byte accesses).
 __global__ void gated_unit_bf16x8_kernel(const __nv_bfloat16* in, int ldi, __nv_bfloat16* __restrict__ out, int ldo, int F,
-                                         int n) {
+                                         int n, int act, float limit) {
   pdl_wait();
   pdl_trigger();
   in = after_wait(in);
@@ -38,25 +40,25 @@ __global__ void gated_unit_bf16x8_kernel(const __nv_bfloat16* in, int ldi, __nv_
   unpack8(*reinterpret_cast<const uint4*>(row + j), g);
   unpack8(*reinterpret_cast<const uint4*>(row + F + j), u);
 #pragma unroll
-  for (int e = 0; e < 8; ++e) o[e] = silu_f(g[e]) * u[e];
+  for (int e = 0; e < 8; ++e) o[e] = mlxb_gated_unit(act, g[e], u[e], 1.f, limit);
   *reinterpret_cast<uint4*>(out + (size_t)t * ldo + j) = pack8(o);
 }
 
-MLXB_EXPORT int mlxb_gated_unit(int dtype, const void* in, int ldi, void* out, int ldo, int F, int n_rows,
-                                cudaStream_t stream) {
+MLXB_EXPORT int mlxb_gated_unit(int dtype, const void* in, int ldi, void* out, int ldo, int F, int n_rows, int act,
+                                float limit, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (F <= 0 || ldi < 2 * F || ldo < F) return mlxb_fail(MLXB_BAD_ARG, "gated_unit: %d columns, strides %d / %d", F, ldi, ldo);
   const long long total = (long long)n_rows * F;
   const int threads = 256;
   const dim3 grid((unsigned)((total + threads - 1) / threads));
   if (dtype == MLXB_F32)
-    launch_pdl(gated_unit_kernel<float>, grid, dim3(threads), 0, stream, (const float*)in, ldi, (float*)out, ldo, F, n_rows);
+    launch_pdl(gated_unit_kernel<float>, grid, dim3(threads), 0, stream, (const float*)in, ldi, (float*)out, ldo, F, n_rows, act, limit);
   else if (dtype == MLXB_BF16 && F % 8 == 0 && ldi % 8 == 0 && ldo % 8 == 0 && (((uintptr_t)in | (uintptr_t)out) & 15) == 0)
     launch_pdl(gated_unit_bf16x8_kernel, dim3((unsigned)((total / 8 + threads - 1) / threads)), dim3(threads), 0, stream,
-               (const __nv_bfloat16*)in, ldi, (__nv_bfloat16*)out, ldo, F, n_rows);
+               (const __nv_bfloat16*)in, ldi, (__nv_bfloat16*)out, ldo, F, n_rows, act, limit);
   else if (dtype == MLXB_BF16)
     launch_pdl(gated_unit_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, (const __nv_bfloat16*)in, ldi,
-               (__nv_bfloat16*)out, ldo, F, n_rows);
+               (__nv_bfloat16*)out, ldo, F, n_rows, act, limit);
   else
     return mlxb_fail(MLXB_BAD_DTYPE, "gated_unit: dtype code %d", dtype);
   return mlxb_check_launch("gated_unit");

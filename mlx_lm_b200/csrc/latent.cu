@@ -7,7 +7,8 @@
 //                 becomes the token's row in the pages (one "head", Dh >= R + dr wide).  Of every query head
 //                 ([d unrotated | dr rotated] in the projection) the rotated part is rotated the same way and put,
 //                 in float32, behind the R columns that head_linear fills: q_lat[t, h] = [W_uk_h^T q_h | rotated q].
-//                 Pairs of a rotation: (2i, 2i+1) (`interleaved`) or (i, i + dr/2); angle p * freq[i], float32.
+//                 Pairs of a rotation: (2i, 2i+1) (`interleaved`) or (i, i + dr/2); angle p * freq[i], float32; cosine
+//                 and sine both times `mscale` (what a stretched rotation multiplies them with; 1: a plain one).
 // head_linear     out[t, h, n] = sum_k x[t, h, k] * w[h, n, k]: a product per head, each head with its own matrix.
 //                 Absorbs the keys' up-projection into the queries (q_h -> W_uk_h^T q_h, so that scores are taken
 //                 against the latent rows directly) and applies the values' up-projection to the attention's output
@@ -23,7 +24,8 @@ __global__ void latent_prepare_kernel(const T* proj, int ld, int q_off, int c_of
                                       int interleaved, const int* __restrict__ positions,
                                       const int* __restrict__ token_req, const int* __restrict__ block_table,
                                       int max_pages, int n_pages, int page, int Dh, T* __restrict__ pool, int write,
-                                      float* __restrict__ q_lat, int ldq, int qhs, int* __restrict__ status) {
+                                      float* __restrict__ q_lat, int ldq, int qhs, int* __restrict__ status,
+                                      float mscale) {
   __shared__ float red[33];
   const int t = blockIdx.x;
   const int r = token_req[t];
@@ -57,6 +59,8 @@ __global__ void latent_prepare_kernel(const T* proj, int ld, int q_off, int c_of
     const float u = to_f(src[lo]), v = to_f(src[hi]);
     float sn, cs;
     sincosf(fp * freq[i], &sn, &cs);
+    cs *= mscale;
+    sn *= mscale;
     const float a = u * cs - v * sn, b = v * cs + u * sn;
     if (hh < H) {
       float* dst = q_lat + (size_t)t * ldq + (size_t)hh * qhs + R;
@@ -79,7 +83,7 @@ MLXB_EXPORT int mlxb_latent_prepare(int dtype, const void* proj, int ld, int q_o
                                     const float* w, float eps, const float* freq, int interleaved, const int* positions,
                                     const int* token_req, const int* block_table, int max_pages, int n_pages, int page,
                                     int Dh, void* pool, int write, float* q_lat, int ldq, int qhs, int n_tokens,
-                                    int* status, cudaStream_t stream) {
+                                    int* status, float mscale, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (H <= 0 || d < 0 || dr < 0 || dr % 2 || R <= 0 || Dh < R + dr || qhs < R + dr || page <= 0 || (dr > 0 && !freq))
     return mlxb_fail(MLXB_BAD_ARG, "latent_prepare: %d heads of %d + %d, %d latent columns in rows of %d", H, d, dr, R, Dh);
@@ -87,11 +91,11 @@ MLXB_EXPORT int mlxb_latent_prepare(int dtype, const void* proj, int ld, int q_o
   if (dtype == MLXB_F32)
     launch_pdl(latent_prepare_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, (const float*)proj, ld, q_off,
                c_off, H, d, dr, R, w, eps, freq, interleaved, positions, token_req, block_table, max_pages, n_pages, page,
-               Dh, (float*)pool, write, q_lat, ldq, qhs, status);
+               Dh, (float*)pool, write, q_lat, ldq, qhs, status, mscale);
   else if (dtype == MLXB_BF16)
     launch_pdl(latent_prepare_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, stream,
                (const __nv_bfloat16*)proj, ld, q_off, c_off, H, d, dr, R, w, eps, freq, interleaved, positions, token_req,
-               block_table, max_pages, n_pages, page, Dh, (__nv_bfloat16*)pool, write, q_lat, ldq, qhs, status);
+               block_table, max_pages, n_pages, page, Dh, (__nv_bfloat16*)pool, write, q_lat, ldq, qhs, status, mscale);
   else
     return mlxb_fail(MLXB_BAD_DTYPE, "latent_prepare: dtype code %d", dtype);
   return mlxb_check_launch("latent_prepare");

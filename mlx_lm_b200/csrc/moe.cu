@@ -2,7 +2,10 @@
 //
 // moe_route   one warp per token: scores s = f(router logits) in float32 (f: sigmoid, or a softmax over the experts),
 //             the `top` largest (ties: the lower expert), their scores as weights (optionally divided by their sum).
-//             sel_expert[t * top + c], sel_weight[t * top + c]; a row that pads the step gets expert -1.
+//             sel_expert[t * top + c], sel_weight[t * top + c]; a row that pads the step gets expert -1.  Options: a
+//             correction per expert added to the scores for the choice only; groups of neighbouring experts of which
+//             only the best few stay in the race; identity experts (no tensors; marked -2); weights scaled.
+// moe_combine x[t] += the sum of the token's choices' rows, an identity expert's choice being its weight times the input.
 // moe_plan    one CTA: the (token, choice) slots sorted by expert, and a list of tiles of at most `tile_rows` slots of
 //             one expert each: tile_info[i] = (expert, first place in the sorted list, slots).  How many tiles there are
 //             depends on the data; the kernels that follow are launched for the most there can be and read the count.
@@ -11,30 +14,39 @@
 //             a token's choices, the slot's own row where it is not).  GATED: W holds [gate | up] rows (2 N of them);
 //             with the routing weight w of the slot the result is silu(w g) * (w u), which is what the gated unit
 //             makes of the expert's input scaled by w (the products are linear in it, so w is applied to the float32
-//             sums instead of to the rounded input).  bfloat16 runs on tensor cores (mma.sync m16n8k16, float32
+//             sums instead of to the rounded input), or the bounded unit times w (gated_unit.cuh).  bfloat16 runs on tensor cores (mma.sync m16n8k16, float32
 //             accumulation; 64 x 64 tiles, 16-byte cp.async in two stages), float32 (and inner sizes that are no
 //             multiple of 8) on the CUDA cores with float32 FMAs in the order of k.  A step of a few tokens (decoding)
 //             takes tiles of 4 slots and a warp per output column instead (moe_rows_kernel).
 // A slot's result does not depend on which tile it lands in or on its place there: every output element is a sum over
 // k in a fixed order.  The sum over a token's choices is taken by the caller in the order of the choices.
 #include "common.cuh"
+#include "gated_unit.cuh"
 
 MLXB_DEFINE_LAST_ERROR()
 
 enum { MOE_SIGMOID = 0, MOE_SOFTMAX = 1 };
 
+// Shared memory: per warp E scores, E choice scores, n_groups group maxima and n_groups flags.
 __global__ void moe_route_kernel(const float* logits, int ldl, const int* __restrict__ token_req, int T, int E, int top,
-                                 int score, int renorm, int* __restrict__ sel_expert, float* __restrict__ sel_weight) {
+                                 int score, int renorm, int* __restrict__ sel_expert, float* __restrict__ sel_weight,
+                                 const float* __restrict__ correction, int n_groups, int keep_groups, int n_real,
+                                 float renorm_eps, float out_scale) {
+  extern __shared__ float mr_smem[];
   pdl_wait();
   pdl_trigger();
   logits = after_wait(logits);
-  const int lane = threadIdx.x & 31;
-  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int t = blockIdx.x * (blockDim.x >> 5) + warp;
   if (t >= T) return;
   if (token_req && token_req[t] < 0) {
     for (int c = lane; c < top; c += 32) { sel_expert[(size_t)t * top + c] = -1; sel_weight[(size_t)t * top + c] = 0.f; }
     return;
   }
+  float* sS = mr_smem + (size_t)warp * (2 * E + 2 * n_groups);     // [E] scores
+  float* sC = sS + E;                                              // [E] what the choice goes by
+  float* sG = sC + E;                                              // [n_groups] the largest choice score of a group
+  int* sKeep = reinterpret_cast<int*>(sG + n_groups);              // [n_groups] is the group among the best?
   const float* z = logits + (size_t)t * ldl;
   float zmax = -INFINITY, zsum = 1.f;
   if (score == MOE_SOFTMAX) {
@@ -44,15 +56,49 @@ __global__ void moe_route_kernel(const float* logits, int ldl, const int* __rest
     for (int e = lane; e < E; e += 32) s += expf(z[e] - zmax);
     zsum = warp_sum(s);
   }
+  for (int e = lane; e < E; e += 32) {
+    const float s = score == MOE_SOFTMAX ? expf(z[e] - zmax) / zsum : 1.f / (1.f + expf(-z[e]));
+    sS[e] = s;
+    sC[e] = correction ? s + correction[e] : s;
+  }
+  __syncwarp();
+  if (n_groups > 1 && keep_groups < n_groups) {
+    // groups of neighbours: only experts of the keep_groups groups with the largest best choice score stay in the race
+    const int per = E / n_groups;
+    for (int g = lane; g < n_groups; g += 32) {
+      float m = -INFINITY;
+      for (int i = 0; i < per; ++i) m = fmaxf(m, sC[g * per + i]);
+      sG[g] = m;
+      sKeep[g] = 0;
+    }
+    __syncwarp();
+    for (int c = 0; c < keep_groups; ++c) {
+      float best = -INFINITY;
+      int best_g = 0x7fffffff;
+      for (int g = lane; g < n_groups; g += 32)
+        if (!sKeep[g] && (sG[g] > best || (sG[g] == best && g < best_g))) { best = sG[g]; best_g = g; }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int og = __shfl_xor_sync(0xffffffffu, best_g, o);
+        if (ob > best || (ob == best && og < best_g)) { best = ob; best_g = og; }
+      }
+      if (lane == 0 && best_g < n_groups) sKeep[best_g] = 1;
+      __syncwarp();
+    }
+    for (int e = lane; e < E; e += 32)
+      if (!sKeep[e / per]) sC[e] = -INFINITY;
+    __syncwarp();
+  }
   float last_s = INFINITY;
   int last_e = -1;
   float wsum = 0.f;
   for (int c = 0; c < top; ++c) {
-    // the largest score that comes after (last_s, last_e) in the order (score descending, expert ascending)
+    // the largest choice score that comes after (last_s, last_e) in the order (score descending, expert ascending)
     float best = -INFINITY;
     int best_e = 0x7fffffff;
     for (int e = lane; e < E; e += 32) {
-      const float s = score == MOE_SOFTMAX ? expf(z[e] - zmax) / zsum : 1.f / (1.f + expf(-z[e]));
+      const float s = sC[e];
       const bool after = s < last_s || (s == last_s && e > last_e);
       if (after && (s > best || (s == best && e < best_e))) { best = s; best_e = e; }
     }
@@ -64,27 +110,86 @@ __global__ void moe_route_kernel(const float* logits, int ldl, const int* __rest
     }
     last_s = best;
     last_e = best_e;
-    wsum += best;
+    const float w = best_e < E ? sS[best_e] : 0.f;      // the weight is the score itself, whatever the choice went by
+    wsum += w;
     if (lane == 0) {
-      sel_expert[(size_t)t * top + c] = best_e < E ? best_e : -1;
-      sel_weight[(size_t)t * top + c] = best;
+      // an expert from n_real on has no tensors (its output is its input): marked -2, which the plan passes over
+      sel_expert[(size_t)t * top + c] = best_e < n_real ? best_e : (best_e < E ? -2 : -1);
+      sel_weight[(size_t)t * top + c] = w;
     }
   }
+  __syncwarp();
   if (renorm) {
-    __syncwarp();
-    for (int c = lane; c < top; c += 32) sel_weight[(size_t)t * top + c] /= wsum;
+    const float d = wsum + renorm_eps;
+    for (int c = lane; c < top; c += 32) sel_weight[(size_t)t * top + c] = sel_weight[(size_t)t * top + c] / d * out_scale;
+  } else if (out_scale != 1.f) {
+    for (int c = lane; c < top; c += 32) sel_weight[(size_t)t * top + c] *= out_scale;
   }
 }
 
+// correction: float32 [E] added to the scores for the choice only, or null; n_groups > 1: the experts form n_groups
+// equal groups of neighbours of which the keep_groups best (by their largest choice score) stay in the race; n_real:
+// experts n_real .. E-1 are identity experts, chosen like the others and marked -2 in sel_expert; renorm: the weights
+// are divided by (their sum + renorm_eps); every weight is multiplied by out_scale.
 MLXB_EXPORT int mlxb_moe_route(const float* logits, int ldl, const int* token_req, int T, int E, int top, int score,
-                               int renorm, int* sel_expert, float* sel_weight, cudaStream_t stream) {
+                               int renorm, int* sel_expert, float* sel_weight, const float* correction, int n_groups,
+                               int keep_groups, int n_real, float renorm_eps, float out_scale, cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (E <= 0 || top <= 0 || top > E || ldl < E || score < 0 || score > 1)
-    return mlxb_fail(MLXB_BAD_ARG, "moe_route: %d of %d experts, score %d", top, E, score);
-  const int warps = 4;
-  launch_pdl(moe_route_kernel, dim3((T + warps - 1) / warps), dim3(32 * warps), 0, stream, logits, ldl, token_req, T, E,
-             top, score, renorm, sel_expert, sel_weight);
+  if (E <= 0 || top <= 0 || top > E || ldl < E || score < 0 || score > 1 || n_groups < 1 || E % n_groups ||
+      keep_groups < 1 || keep_groups > n_groups || n_real < 0 || n_real > E || top > keep_groups * (E / n_groups))
+    return mlxb_fail(MLXB_BAD_ARG, "moe_route: %d of %d experts (%d with tensors), score %d, %d of %d groups", top, E,
+                     n_real, score, keep_groups, n_groups);
+  const size_t per_warp = sizeof(float) * (2 * (size_t)E + 2 * (size_t)n_groups);
+  if (per_warp > 48 * 1024) return mlxb_fail(MLXB_BAD_ARG, "moe_route: %d experts are more than a warp keeps", E);
+  const int warps = 4 * per_warp <= 48 * 1024 ? 4 : 1;
+  launch_pdl(moe_route_kernel, dim3((T + warps - 1) / warps), dim3(32 * warps), warps * per_warp, stream, logits, ldl,
+             token_req, T, E, top, score, renorm, sel_expert, sel_weight, correction, n_groups, keep_groups, n_real,
+             renorm_eps, out_scale);
   return mlxb_check_launch("moe_route");
+}
+
+// x[t] += sum over the token's choices, in their order: the expert's row y[t * top + c] for a choice with tensors,
+// sel_weight * h[t] for an identity expert (sel_expert -2).  Rows that pad the step are passed over.
+template <typename T>
+__global__ void moe_combine_kernel(float* x, int ldx, const float* y, int ldy, const int* sel_expert,
+                                   const float* sel_weight, const T* h, int ldh, const int* __restrict__ token_req,
+                                   int top, int D) {
+  pdl_wait();
+  pdl_trigger();
+  x = after_wait(x);
+  y = after_wait(y);
+  sel_expert = after_wait(sel_expert);
+  sel_weight = after_wait(sel_weight);
+  h = after_wait(h);
+  const int t = blockIdx.x;
+  if (token_req && token_req[t] < 0) return;
+  for (int c = threadIdx.x; c < D; c += blockDim.x) {
+    float acc = 0.f;
+    for (int k = 0; k < top; ++k) {
+      const int slot = t * top + k, e = sel_expert[slot];
+      if (e >= 0) acc += y[(size_t)slot * ldy + c];
+      else if (e == -2) acc = fmaf(sel_weight[slot], to_f(h[(size_t)t * ldh + c]), acc);
+    }
+    x[(size_t)t * ldx + c] += acc;
+  }
+}
+
+MLXB_EXPORT int mlxb_moe_combine(int dtype, float* x, int ldx, const float* y, int ldy, const int* sel_expert,
+                                 const float* sel_weight, const void* h, int ldh, const int* token_req, int T, int top,
+                                 int D, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (D <= 0 || top <= 0 || ldx < D || ldy < D || ldh < D)
+    return mlxb_fail(MLXB_BAD_ARG, "moe_combine: width %d, %d choices, strides %d / %d / %d", D, top, ldx, ldy, ldh);
+  const int threads = D >= 1024 ? 256 : (D >= 256 ? 128 : 64);
+  if (dtype == MLXB_F32)
+    launch_pdl(moe_combine_kernel<float>, dim3(T), dim3(threads), 0, stream, x, ldx, y, ldy, sel_expert, sel_weight,
+               (const float*)h, ldh, token_req, top, D);
+  else if (dtype == MLXB_BF16)
+    launch_pdl(moe_combine_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, x, ldx, y, ldy, sel_expert,
+               sel_weight, (const __nv_bfloat16*)h, ldh, token_req, top, D);
+  else
+    return mlxb_fail(MLXB_BAD_DTYPE, "moe_combine: dtype code %d", dtype);
+  return mlxb_check_launch("moe_combine");
 }
 
 // sorted [S]; tile_info [max_tiles][3]; n_tiles [1].  Shared memory: 3 E + 1 ints.
@@ -135,8 +240,6 @@ MLXB_EXPORT int mlxb_moe_plan(const int* sel_expert, int S, int E, int tile_rows
   return mlxb_check_launch("moe_plan");
 }
 
-__device__ __forceinline__ float silu_f(float v) { return v / (1.f + expf(-v)); }
-
 // ---------------------------------------------------------------- CUDA cores: any sizes, float32 or bfloat16 inputs
 constexpr int MS_BM = 16, MS_BN = 64, MS_BK = 32, MS_THREADS = 256;
 
@@ -144,7 +247,7 @@ template <typename T, typename TO, bool GATED>
 __global__ void __launch_bounds__(MS_THREADS)
 moe_gemm_simt_kernel(const T* A, int lda, int a_div, const T* __restrict__ W, long long w_stride, int N, int K,
                      const int* sorted, const int* tile_info, const int* n_tiles, const float* sel_weight,
-                     TO* __restrict__ out, int ldo) {
+                     TO* __restrict__ out, int ldo, int act, float limit) {
   __shared__ float sA[MS_BM][MS_BK + 1];
   __shared__ float sW[GATED ? 2 : 1][MS_BN][MS_BK + 1];
   __shared__ int sSlot[MS_BM];
@@ -198,7 +301,7 @@ moe_gemm_simt_kernel(const T* A, int lda, int a_div, const T* __restrict__ W, lo
     const int n = n0 + cb + 16 * i;
     if (n >= N) continue;
     float v = acc[0][i];
-    if (GATED) v = silu_f(w * acc[0][i]) * (w * acc[GATED ? 1 : 0][i]);
+    if (GATED) v = mlxb_gated_unit(act, acc[0][i], acc[GATED ? 1 : 0][i], w, limit);
     out[(size_t)slot * ldo + n] = from_f<TO>(v);
   }
 }
@@ -214,7 +317,7 @@ template <typename TO, bool GATED>
 __global__ void __launch_bounds__(MV_THREADS)
 moe_rows_kernel(const __nv_bfloat16* A, int lda, int a_div, const __nv_bfloat16* __restrict__ W, long long w_stride, int N,
                 int K, const int* sorted, const int* tile_info, const int* n_tiles, const float* sel_weight,
-                TO* __restrict__ out, int ldo) {
+                TO* __restrict__ out, int ldo, int act, float limit) {
   extern __shared__ uint4 mv_rows[];          // [MV_ROWS][K / 8]
   __shared__ int sSlot[MV_ROWS];
   pdl_wait();
@@ -277,8 +380,7 @@ moe_rows_kernel(const __nv_bfloat16* A, int lda, int a_div, const __nv_bfloat16*
         for (int rr = 0; rr < MV_ROWS; ++rr)
           if (rr == lane) { v = acc[0][rr]; v2 = acc[GATED ? 1 : 0][rr]; }
         if (GATED) {
-          const float w = sel_weight[slot];
-          v = silu_f(w * v) * (w * v2);
+          v = mlxb_gated_unit(act, v, v2, sel_weight[slot], limit);
         }
         out[(size_t)slot * ldo + n] = from_f<TO>(v);
       }
@@ -310,7 +412,7 @@ template <typename TO, bool GATED>
 __global__ void __launch_bounds__(MG_THREADS)
 moe_gemm_tc_kernel(const __nv_bfloat16* A, int lda, int a_div, const __nv_bfloat16* __restrict__ W, long long w_stride,
                    int N, int K, const int* sorted, const int* tile_info, const int* n_tiles, const float* sel_weight,
-                   TO* __restrict__ out, int ldo) {
+                   TO* __restrict__ out, int ldo, int act, float limit) {
   constexpr int NH = GATED ? 2 : 1;
   __shared__ __align__(16) __nv_bfloat16 sA[2][MG_BM][MG_LD];
   __shared__ __align__(16) __nv_bfloat16 sW[2][NH][MG_BN][MG_LD];
@@ -391,7 +493,7 @@ moe_gemm_tc_kernel(const __nv_bfloat16* A, int lda, int a_div, const __nv_bfloat
         const int n = n0 + j * 8 + q4 * 2 + x;
         if (n >= N) continue;
         float v = acc[0][j][half * 2 + x];
-        if (GATED) v = silu_f(w * v) * (w * acc[NH - 1][j][half * 2 + x]);
+        if (GATED) v = mlxb_gated_unit(act, v, acc[NH - 1][j][half * 2 + x], w, limit);
         out[(size_t)slot * ldo + n] = from_f<TO>(v);
       }
   }
@@ -407,7 +509,7 @@ MLXB_EXPORT int mlxb_moe_tile_rows(int tensor_cores) { return tensor_cores == 2 
 MLXB_EXPORT int mlxb_moe_gemm(int dtype, int out_f32, int gated, const void* A, int lda, int a_div, const void* W,
                               long long w_stride, int N, int K, const int* sorted, const int* tile_info,
                               const int* n_tiles, int max_tiles, int tile_rows, const float* sel_weight, void* out,
-                              int ldo, cudaStream_t stream) {
+                              int ldo, int act, float limit, cudaStream_t stream) {
   if (max_tiles <= 0) return 0;
   if (N <= 0 || K <= 0 || a_div <= 0 || lda < K || ldo < N || (gated && !sel_weight) ||
       (tile_rows != MG_BM && tile_rows != MS_BM && tile_rows != MV_ROWS) ||
@@ -415,11 +517,11 @@ MLXB_EXPORT int mlxb_moe_gemm(int dtype, int out_f32, int gated, const void* A, 
     return mlxb_fail(MLXB_BAD_ARG, "moe_gemm: %d x %d, strides %d / %d, tiles of %d rows", N, K, lda, ldo, tile_rows);
 #define MOE_SIMT(T, TO, G)                                                                                             \
   launch_pdl(moe_gemm_simt_kernel<T, TO, G>, dim3(max_tiles, (N + MS_BN - 1) / MS_BN), dim3(MS_THREADS), 0, stream,    \
-             (const T*)A, lda, a_div, (const T*)W, w_stride, N, K, sorted, tile_info, n_tiles, sel_weight, (TO*)out, ldo)
+             (const T*)A, lda, a_div, (const T*)W, w_stride, N, K, sorted, tile_info, n_tiles, sel_weight, (TO*)out, ldo, act, limit)
 #define MOE_TC(TO, G)                                                                                                  \
   launch_pdl(moe_gemm_tc_kernel<TO, G>, dim3(max_tiles, (N + MG_BN - 1) / MG_BN), dim3(MG_THREADS), 0, stream,         \
              (const __nv_bfloat16*)A, lda, a_div, (const __nv_bfloat16*)W, w_stride, N, K, sorted, tile_info, n_tiles, \
-             sel_weight, (TO*)out, ldo)
+             sel_weight, (TO*)out, ldo, act, limit)
   if (dtype == MLXB_F32) {
     if (gated) MOE_SIMT(float, float, true); else MOE_SIMT(float, float, false);
   } else if (dtype == MLXB_BF16) {
@@ -432,7 +534,7 @@ MLXB_EXPORT int mlxb_moe_gemm(int dtype, int out_f32, int gated, const void* A, 
 #define MOE_ROWS(TO, G)                                                                                                \
   launch_pdl(moe_rows_kernel<TO, G>, dim3(max_tiles, (N + MV_COLS - 1) / MV_COLS), dim3(MV_THREADS), smem, stream,     \
              (const __nv_bfloat16*)A, lda, a_div, (const __nv_bfloat16*)W, w_stride, N, K, sorted, tile_info, n_tiles, \
-             sel_weight, (TO*)out, ldo)
+             sel_weight, (TO*)out, ldo, act, limit)
       if (gated) { if (out_f32) MOE_ROWS(float, true); else MOE_ROWS(__nv_bfloat16, true); }
       else { if (out_f32) MOE_ROWS(float, false); else MOE_ROWS(__nv_bfloat16, false); }
 #undef MOE_ROWS

@@ -21,6 +21,7 @@
 // A slot's result does not depend on which tile it lands in or on its place there: the sum over K runs stage by
 // stage in a fixed order.
 #include "tcgen05.cuh"
+#include "gated_unit.cuh"
 
 MLXB_DEFINE_LAST_ERROR()
 
@@ -44,7 +45,6 @@ struct MoeSmem {
   int abort_flag;
 };
 
-__device__ __forceinline__ float mt_silu(float v) { return v / (1.f + expf(-v)); }
 
 // dst [*, ldd] <- src [*, lds], `cols` columns (a multiple of 8): one warp a row, 16 bytes a lane and step.
 __global__ void moe_gather_kernel(const __nv_bfloat16* src, int lds, int a_div, const int* sorted, const int* tile_info,
@@ -80,7 +80,8 @@ template <bool GATED, int BN>
 __global__ void __launch_bounds__(MT_THREADS)
 moe_gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                      const int* sorted, const int* tile_info, const int* n_tiles_p, int NW, int N, int K,
-                     const float* sel_weight, void* out_v, int ldo, int* __restrict__ status) {
+                     const float* sel_weight, void* out_v, int ldo, int* __restrict__ status, int act,
+                     float limit) {
   extern __shared__ uint8_t smem_raw[];
   MoeSmem<BN>& sm = *reinterpret_cast<MoeSmem<BN>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   constexpr int MT_BN = BN, MT_STAGES = mt_stages(BN), HALF = BN / 2;
@@ -217,7 +218,7 @@ moe_gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
               float v[8];
 #pragma unroll
               for (int i = 0; i < 8; ++i)
-                v[i] = mt_silu(wgt * __uint_as_float(g[8 * g8 + i])) * (wgt * __uint_as_float(u[8 * g8 + i]));
+                v[i] = mlxb_gated_unit(act, __uint_as_float(g[8 * g8 + i]), __uint_as_float(u[8 * g8 + i]), wgt, limit);
               *reinterpret_cast<uint4*>(o + n8) = pack8(v);
             }
           }
@@ -312,6 +313,8 @@ struct MtLaunch {
   int* status;
   int max_tiles;
   cudaStream_t stream;
+  int act;
+  float limit;
 };
 
 template <bool GATED, int BN>
@@ -330,7 +333,7 @@ static int mt_launch(const MtLaunch& l) {
   const long long work = (long long)l.max_tiles * ((l.N + cols - 1) / cols);
   const dim3 grid((unsigned)(work < mt_sm_count() ? work : mt_sm_count()));
   launch_pdl(kern, grid, dim3(MT_THREADS), smem, l.stream, l.ma, l.mw, l.sorted, l.tile_info, l.n_tiles, l.NW, l.N, l.K,
-             l.sel_weight, l.out, l.ldo, l.status);
+             l.sel_weight, l.out, l.ldo, l.status, l.act, l.limit);
   return mlxb_check_launch("moe_gemm (tensor cores)");
 }
 
@@ -368,18 +371,19 @@ static int mt_tile_width(int S, int E, int N, bool gated) {
 }
 
 // A: bfloat16 [S, lda], rows in the plan's order; W: bfloat16 [E][NW][K] contiguous, NW = 2 N (gated: gate rows, then up
-// rows) or N.  gated: out bfloat16 [S, ldo] in the plan's order = silu(w g) * (w u); else out float32 [S, ldo], row
+// rows) or N.  gated: out bfloat16 [S, ldo] in the plan's order = the gated unit of kind `act` (gated_unit.cuh); else out float32 [S, ldo], row
 // sorted[i] = the product of row i.  The plan was made with tiles of mlxb_moe_tc05_tile_rows() slots.
 // K, N, lda, ldo multiples of 8; A, W, out 16-byte aligned.
 MLXB_EXPORT int mlxb_moe_gemm_tc05(int gated, const void* A, int lda, int S, const void* W, int E, int NW, int N, int K,
                                    const int* sorted, const int* tile_info, const int* n_tiles, int max_tiles,
-                                   const float* sel_weight, void* out, int ldo, int* status, cudaStream_t stream) {
+                                   const float* sel_weight, void* out, int ldo, int* status, int act, float limit,
+                                   cudaStream_t stream) {
   if (max_tiles <= 0 || S <= 0) return 0;
   if (N <= 0 || K <= 0 || E <= 0 || (K & 7) || (N & 7) || (lda & 7) || (ldo & 7) || lda < K || ldo < N ||
       NW != (gated ? 2 : 1) * N || (gated && !sel_weight) || (((uintptr_t)A | (uintptr_t)W | (uintptr_t)out) & 15) ||
       (long long)E * NW > 0x7fffffffLL)
     return mlxb_fail(MLXB_BAD_ARG, "moe_gemm (tensor cores): %d experts of %d x %d, strides %d / %d", E, NW, K, lda, ldo);
-  MtLaunch l = {{}, {}, sorted, tile_info, n_tiles, NW, N, K, sel_weight, out, ldo, status, max_tiles, stream};
+  MtLaunch l = {{}, {}, sorted, tile_info, n_tiles, NW, N, K, sel_weight, out, ldo, status, max_tiles, stream, act, limit};
   if (int e = mt_make_map(&l.ma, A, S, K, lda, MT_BM)) return e;
   if (int e = mt_make_map(&l.mw, W, (long long)E * NW, K, K, 64)) return e;
   const int bn = mt_tile_width(S, E, N, gated != 0);

@@ -6,7 +6,8 @@
 // a recurrence (step sizes, decays, gates, unit norms) is float32; inputs arrive in the activation
 // dtype.  The order of additions for a token depends on the layer's sizes only, never on the batch.
 //
-// conv_silu          out[t, c] = silu(bias[c] + sum_j w[c, taps-1-j] * in(t - j, c)),  j = 0 .. taps-1,
+// conv_silu          out[t, c] = silu(bias[c] + sum_j w[c, taps-1-j] * in(t - j, c)),  j = 0 .. taps-1 (act = 0: the sum
+//                    as it is, without the silu),
 //                    where in(t - j) is a row of this step if the run reaches that far back, else one of
 //                    the request's last taps-1 inputs kept in the state (zeros before the sequence starts).
 // conv_state_update  moves the last taps-1 inputs of every run into the state (launched after conv_silu).
@@ -43,7 +44,7 @@ template <typename T>
 __global__ void conv_silu_kernel(const T* in, int ldi, const float* __restrict__ w, const float* __restrict__ bias,
                                  int taps, int C, const float* state, const int* __restrict__ slots,
                                  const int* __restrict__ positions, const int* __restrict__ token_req,
-                                 const int* __restrict__ req_first_position, T* __restrict__ out, int ldo) {
+                                 const int* __restrict__ req_first_position, T* __restrict__ out, int ldo, int act) {
   const int t = blockIdx.y, c = blockIdx.x * blockDim.x + threadIdx.x;
   const int r = token_req[t];
   if (r < 0 || c >= C) return;
@@ -60,7 +61,7 @@ __global__ void conv_silu_kernel(const T* in, int ldi, const float* __restrict__
     else v = state[((size_t)slot * (taps - 1) + (taps - 1 + i - j)) * C + c];
     acc = fmaf(w[(size_t)c * taps + taps - 1 - j], v, acc);
   }
-  out[(size_t)t * ldo + c] = from_f<T>(silu_f(acc));
+  out[(size_t)t * ldo + c] = from_f<T>(act ? silu_f(acc) : acc);
 }
 
 // The same with VEC = 16 / sizeof(T) neighbouring channels a thread and 16-byte accesses (C, the strides and the
@@ -88,7 +89,7 @@ template <typename T>
 __global__ void conv_silu_vec_kernel(const T* in, int ldi, const float* __restrict__ wt, const float* __restrict__ bias,
                                      int taps, int C, const float* state, const int* __restrict__ slots,
                                      const int* __restrict__ positions, const int* __restrict__ token_req,
-                                     const int* __restrict__ req_first_position, T* __restrict__ out, int ldo) {
+                                     const int* __restrict__ req_first_position, T* __restrict__ out, int ldo, int act) {
   constexpr int VEC = Vec16<T>::N;
   const int t = blockIdx.y, c = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
   const int r = token_req[t];
@@ -125,7 +126,7 @@ __global__ void conv_silu_vec_kernel(const T* in, int ldi, const float* __restri
     }
   }
 #pragma unroll
-  for (int e = 0; e < VEC; ++e) acc[e] = silu_f(acc[e]);
+  for (int e = 0; e < VEC; ++e) acc[e] = act ? silu_f(acc[e]) : acc[e];
   Vec16<T>::store(out + (size_t)t * ldo + c, acc);
 }
 
@@ -159,7 +160,7 @@ template <typename T>
 static int conv_launch(const void* in, int ldi, const float* w, const float* wt, const float* bias, int taps, int C, float* state,
                        const int* slots, const int* positions, const int* token_req, const int* req_first_token,
                        const int* req_first_position, void* out, int ldo, int n_tokens, int n_requests,
-                       cudaStream_t stream) {
+                       int act, cudaStream_t stream) {
   const int threads = 128;
   constexpr int VEC = 16 / (int)sizeof(T);
   // (with few rows the launch is a matter of latency, and more, lighter threads are the quicker: decode steps of
@@ -169,12 +170,13 @@ static int conv_launch(const void* in, int ldi, const float* w, const float* wt,
   if (vec) {
     const int tv = C / VEC >= 128 ? 128 : 64;
     launch_pdl(conv_silu_vec_kernel<T>, dim3((C / VEC + tv - 1) / tv, n_tokens), dim3(tv), 0, stream, (const T*)in, ldi,
-               wt, bias, taps, C, (const float*)state, slots, positions, token_req, req_first_position, (T*)out, ldo);
+               wt, bias, taps, C, (const float*)state, slots, positions, token_req, req_first_position, (T*)out, ldo, act);
   } else {
     launch_pdl(conv_silu_kernel<T>, dim3((C + threads - 1) / threads, n_tokens), dim3(threads), 0, stream, (const T*)in,
-               ldi, w, bias, taps, C, (const float*)state, slots, positions, token_req, req_first_position, (T*)out, ldo);
+               ldi, w, bias, taps, C, (const float*)state, slots, positions, token_req, req_first_position, (T*)out, ldo, act);
   }
   if (int e = mlxb_check_launch("conv_silu")) return e;
+  if (taps == 1) return 0;          // nothing of earlier tokens is read: no state
   launch_pdl(conv_state_update_kernel<T>, dim3((C + threads - 1) / threads, n_requests), dim3(threads), 0, stream,
              (const T*)in, ldi, taps, C, state, slots, token_req, req_first_token);
   return mlxb_check_launch("conv_state_update");
@@ -182,23 +184,23 @@ static int conv_launch(const void* in, int ldi, const float* w, const float* wt,
 
 // in: [n_tokens, >= C] at row stride ldi (activation dtype); w: float32 [C, taps]; wt: the same tap by tap, float32
 // [taps, C], or null (with it, and sizes that allow 16-byte accesses, the vector kernel runs); bias: float32 [C] or null;
-// state: float32 [slots, taps-1, C]; out: [n_tokens, C] at row stride ldo.  Two launches: the convolution, then the
+// state: float32 [slots, taps-1, C]; out: [n_tokens, C] at row stride ldo; act: 1 silu, 0 none.  Two launches: the convolution, then the
 // state's update (which must not overtake the convolution's reads of the state).
 MLXB_EXPORT int mlxb_conv_silu(int dtype, const void* in, int ldi, const float* w, const float* wt, const float* bias, int taps, int C,
                                float* state, const int* slots, const int* positions, const int* token_req,
                                const int* req_first_token, const int* req_first_position, void* out, int ldo,
-                               int n_tokens, int n_requests, cudaStream_t stream) {
+                               int n_tokens, int n_requests, int act, cudaStream_t stream) {
   if (n_tokens <= 0 || n_requests <= 0) return 0;
-  if (taps < 2 || taps > 9 || C <= 0 || ldi < C || ldo < C || n_tokens > 65535 * 32 || n_requests > 65535)
-    return mlxb_fail(MLXB_BAD_ARG, "conv: %d taps (2..9), %d channels, strides %d / %d, %d tokens of %d requests", taps, C,
+  if (taps < 1 || taps > 9 || C <= 0 || ldi < C || ldo < C || n_tokens > 65535 * 32 || n_requests > 65535)
+    return mlxb_fail(MLXB_BAD_ARG, "conv: %d taps (1..9), %d channels, strides %d / %d, %d tokens of %d requests", taps, C,
                      ldi, ldo, n_tokens, n_requests);
   if (n_tokens > 65535) return mlxb_fail(MLXB_BAD_ARG, "conv: %d tokens are too many for one call", n_tokens);
   if (dtype == MLXB_F32)
     return conv_launch<float>(in, ldi, w, wt, bias, taps, C, state, slots, positions, token_req, req_first_token,
-                              req_first_position, out, ldo, n_tokens, n_requests, stream);
+                              req_first_position, out, ldo, n_tokens, n_requests, act, stream);
   if (dtype == MLXB_BF16)
     return conv_launch<__nv_bfloat16>(in, ldi, w, wt, bias, taps, C, state, slots, positions, token_req, req_first_token,
-                                      req_first_position, out, ldo, n_tokens, n_requests, stream);
+                                      req_first_position, out, ldo, n_tokens, n_requests, act, stream);
   return mlxb_fail(MLXB_BAD_DTYPE, "conv: dtype code %d", dtype);
 }
 

@@ -126,3 +126,47 @@ MLXB_EXPORT int mlxb_residual_update(int cast_dtype, float* x, int ldx, const fl
     return mlxb_fail(MLXB_BAD_DTYPE, "residual_update: dtype code %d", cast_dtype);
   return mlxb_check_launch("residual_update");
 }
+
+// Two score maps over the same values, combined per head: with a1 and a2 the two maps' outputs of head h,
+// o = a1 - lambda * a2, divided by its root mean square over the head's Dv columns (eps inside the root, no weight),
+// times `post`.  a: float32 [T, lda] in which the heads of key/value group g lie as [map 1: rep heads | map 2: rep heads]
+// (head h = g * rep + r has its first map at column ((2 g) rep + r) Dv and its second at ((2 g + 1) rep + r) Dv).
+// One warp per (token, head).
+template <typename TO>
+__global__ void head_difference_kernel(const float* a, int lda, const int* __restrict__ token_req, int H, int rep, int Dv,
+                                       float lambda, float eps, float post, TO* __restrict__ out, int ldo, int T) {
+  pdl_wait();
+  pdl_trigger();
+  a = after_wait(a);
+  const int lane = threadIdx.x & 31;
+  const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (item >= (long long)T * H) return;
+  const int t = (int)(item / H), h = (int)(item - (long long)t * H);
+  if (token_req && token_req[t] < 0) return;
+  const int g = h / rep, r = h - g * rep;
+  const float* a1 = a + (size_t)t * lda + (size_t)((2 * g) * rep + r) * Dv;
+  const float* a2 = a1 + (size_t)rep * Dv;
+  float ss = 0.f;
+  for (int d = lane; d < Dv; d += 32) { const float o = a1[d] - lambda * a2[d]; ss = fmaf(o, o, ss); }
+  const float f = post / sqrtf(warp_sum(ss) / (float)Dv + eps);
+  TO* op = out + (size_t)t * ldo + (size_t)h * Dv;
+  for (int d = lane; d < Dv; d += 32) op[d] = from_f<TO>((a1[d] - lambda * a2[d]) * f);
+}
+
+MLXB_EXPORT int mlxb_head_difference(int out_dtype, const float* a, int lda, const int* token_req, int H, int rep, int Dv,
+                                     float lambda, float eps, float post, void* out, int ldo, int T, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (H <= 0 || rep <= 0 || H % rep || Dv <= 0 || lda < 2 * H * Dv || ldo < H * Dv)
+    return mlxb_fail(MLXB_BAD_ARG, "head_difference: %d heads in groups of %d, %d columns, strides %d / %d", H, rep, Dv, lda, ldo);
+  const int warps = 4;
+  const dim3 grid((unsigned)(((long long)T * H + warps - 1) / warps));
+  if (out_dtype == MLXB_F32)
+    launch_pdl(head_difference_kernel<float>, grid, dim3(32 * warps), 0, stream, a, lda, token_req, H, rep, Dv, lambda, eps,
+               post, (float*)out, ldo, T);
+  else if (out_dtype == MLXB_BF16)
+    launch_pdl(head_difference_kernel<__nv_bfloat16>, grid, dim3(32 * warps), 0, stream, a, lda, token_req, H, rep, Dv,
+               lambda, eps, post, (__nv_bfloat16*)out, ldo, T);
+  else
+    return mlxb_fail(MLXB_BAD_DTYPE, "head_difference: dtype code %d", out_dtype);
+  return mlxb_check_launch("head_difference");
+}

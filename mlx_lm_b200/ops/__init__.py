@@ -805,21 +805,37 @@ def residual_update(x, y1, stream, w1=None, y2=None, w2=None, scale: float = 1.0
           _p(w2), ldy, float(scale), float(eps), _p(cast_out), ldc, R, D, stream)
 
 
+def head_difference(a, rep: int, value_dim: int, lam: float, eps: float, post: float, out, stream, token_req=None) -> None:
+    """Two score maps over the same values combined per head: ``o = a1 - lam * a2``, divided by its root mean square
+    over the head's ``value_dim`` columns (eps inside the root, no weight), times ``post``.  ``a``: float32
+    ``[T, 2 * H * value_dim]`` in which the heads of key/value group ``g`` lie as ``[map 1: rep heads | map 2: rep
+    heads]``; ``out``: ``[T, H * value_dim]`` in the run's dtype or float32, heads in their own order."""
+    _need(a, torch.float32, "head_difference a")
+    T, n = out.shape
+    if n % value_dim or a.shape != (T, 2 * n) or (n // value_dim) % rep:
+        raise KernelError(f"head_difference: a {tuple(a.shape)}, out {tuple(out.shape)}, heads of {value_dim} in groups of {rep}")
+    _call("rms", "mlxb_head_difference", [c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_float, c_float,
+                                          c_void_p, c_int, c_int, c_void_p],
+          dtype_code(out.dtype), _p(a), _rows(a, "head_difference a"), _p(token_req), n // value_dim, int(rep),
+          int(value_dim), float(lam), float(eps), float(post), _p(out), _rows(out, "head_difference out"), T, stream)
+
+
 # --------------------------------------------------------------------------
 # layers with a state of fixed size per request (csrc/recurrent.cu)
 
 _CONV_ARGS = [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-              c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+              c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
 
 
 def conv_silu(x, weight, bias, state, slots, positions, token_req, req_first_token, req_first_position, out,
-              stream, weight_by_tap=None) -> None:
+              stream, weight_by_tap=None, activation: bool = True) -> None:
     """Causal convolution over time per channel, then silu: ``out[t, c] = silu(bias[c] + sum_j weight[c, taps-1-j]
     * x(t - j, c))``.  ``x``: ``[T, C]`` view (contiguous rows); ``weight`` float32 ``[C, taps]`` (last column: the
     current token); ``state`` float32 ``[slots, taps-1, C]``: each request's last inputs, read for the rows that
     reach back before the step and brought up to date afterwards (two launches).  ``weight_by_tap``: the same
     weights as float32 ``[taps, C]`` (a copy the caller keeps); with it, and with sizes that allow 16-byte accesses,
-    a thread takes eight (float32: four) neighbouring channels."""
+    a thread takes eight (float32: four) neighbouring channels.  ``activation=False``: the sum as it is, without the
+    silu.  With one tap there is no state: ``state`` may be any float32 tensor ``[slots, 0, C]``."""
     _need(x, out.dtype, "conv x")
     _need(weight, torch.float32, "conv weight")
     _need(state, torch.float32, "conv state")
@@ -837,7 +853,7 @@ def conv_silu(x, weight, bias, state, slots, positions, token_req, req_first_tok
             raise KernelError(f"conv: weights by tap {tuple(weight_by_tap.shape)} for {taps} taps of {C} channels")
     _call("recurrent", "mlxb_conv_silu", _CONV_ARGS, dtype_code(out.dtype), _p(x), _rows(x, "conv x"), _p(weight),
           _p(weight_by_tap), _p(bias), taps, C, _p(state), _p(slots), _p(positions), _p(token_req), _p(req_first_token),
-          _p(req_first_position), _p(out), _rows(out, "conv out"), T, slots.numel(), stream)
+          _p(req_first_position), _p(out), _rows(out, "conv out"), T, slots.numel(), int(bool(activation)), stream)
 
 
 _M2_ARGS = [c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -892,26 +908,31 @@ def gated_delta_scan(qkv, q_off: int, k_off: int, v_off: int, b_raw, a_raw, dt_b
 
 _QKVP_ARGS = [c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
               c_float, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p,
-              c_void_p, c_int, c_int, c_void_p, c_int, c_float, c_int, c_int, c_void_p]
+              c_void_p, c_int, c_int, c_void_p, c_int, c_float, c_int, c_int, c_int, c_float, c_float, c_void_p]
 
 
 def qkv_prepare(proj, q_off: int, k_off: int, v_off: int, n_heads: int, n_kv_heads: int, dk: int, dv: int, q_norm,
                 k_norm, eps: float, freq, positions, token_req, block_table, k_pool, v_pool, q_out, write: bool, status,
-                stream, interleaved: bool = False, v_norm_eps: Optional[float] = None) -> None:
+                stream, interleaved: bool = False, v_norm_eps: Optional[float] = None, mscale: float = 1.0,
+                head_norm_eps: Optional[float] = None) -> None:
     """From a fused projection ``proj [T, .]``: optional RMS norm over a token's whole q and whole k projection
     (float32 weights ``q_norm``, ``k_norm`` or None), rotation of the first ``2 * len(freq)`` dimensions of every
     head by the token's position (pairs ``(i, i + len(freq))``; ``freq`` float32 or None), q into ``q_out
     [T, n_heads*Dh]``, k and v into the pages ``[n_pages, n_kv_heads, page, Dh]`` (values: their own row width); columns of a head beyond
     ``dk`` / ``dv`` are zeros.  ``interleaved``: the pairs are ``(2i, 2i+1)``.  ``v_norm_eps``: every value head is
-    divided by its root mean square (this eps inside the root, no weight) before it enters the page.  ``q_out`` may
+    divided by its root mean square (this eps inside the root, no weight) before it enters the page.  ``mscale``: a
+    factor on every cosine and sine (what a stretched rotation multiplies them with).  ``head_norm_eps``: every q and k
+    head is divided by its root mean square over its ``dk`` columns AFTER the rotation (no weight).  ``v_pool`` may have
+    fewer heads than ``k_pool`` (a divisor of them): the projection then holds that many value heads.  ``q_out`` may
     be float32 in a bfloat16 run."""
     n_pages, Hkv, page, Dh = k_pool.shape
     _need(proj, k_pool.dtype, "qkv_prepare proj")
     if q_out.dtype != torch.float32:
         _need(q_out, k_pool.dtype, "qkv_prepare q_out")
+    Hv = v_pool.shape[1]
     if (Hkv != n_kv_heads or q_out.shape[1] != n_heads * Dh or not (k_pool.is_contiguous() and v_pool.is_contiguous())
-            or v_pool.shape[:3] != k_pool.shape[:3]):
-        raise KernelError(f"qkv_prepare: pools {tuple(k_pool.shape)}, q_out {tuple(q_out.shape)}")
+            or v_pool.shape[0] != n_pages or v_pool.shape[2] != page or Hv <= 0 or Hkv % Hv):
+        raise KernelError(f"qkv_prepare: pools {tuple(k_pool.shape)} and {tuple(v_pool.shape)}, q_out {tuple(q_out.shape)}")
     half = 0
     if freq is not None:
         _need(freq, torch.float32, "qkv_prepare freq")
@@ -926,7 +947,8 @@ def qkv_prepare(proj, q_off: int, k_off: int, v_off: int, n_heads: int, n_kv_hea
           _p(positions), _p(token_req), _p(block_table), block_table.shape[1], n_pages, page, _p(q_out),
           _rows(q_out, "qkv_prepare q_out"), _p(k_pool), _p(v_pool), int(bool(write)), proj.shape[0], _p(status),
           int(bool(interleaved)), -1.0 if v_norm_eps is None else float(v_norm_eps),
-          int(q_out.dtype == torch.float32 and k_pool.dtype != torch.float32), v_pool.shape[3], stream)
+          int(q_out.dtype == torch.float32 and k_pool.dtype != torch.float32), v_pool.shape[3], Hv, float(mscale),
+          -1.0 if head_norm_eps is None else float(head_norm_eps), stream)
 
 
 # --------------------------------------------------------------------------
@@ -934,7 +956,13 @@ def qkv_prepare(proj, q_off: int, k_off: int, v_off: int, n_heads: int, n_kv_hea
 
 _WIDE_ARGS = [c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
               c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
-              c_int, c_void_p, c_int, c_void_p, c_float, c_int, c_int, c_void_p]
+              c_int, c_void_p, c_int, c_void_p, c_float, c_int, c_int, c_int, c_void_p]
+
+
+def _pools_fit(k_pool, v_pool) -> bool:
+    """Key and value pools over the same pages, the value heads as many as the key heads or a divisor of them."""
+    return (v_pool.shape[0] == k_pool.shape[0] and v_pool.shape[2] == k_pool.shape[2] and v_pool.shape[1] > 0
+            and k_pool.shape[1] % v_pool.shape[1] == 0 and k_pool.is_contiguous() and v_pool.is_contiguous())
 
 
 def _wide_gate(gate, dtype, n_heads: int, value_dim: int, what: str):
@@ -959,13 +987,15 @@ def attention_wide(q, q_head_stride: int, positions, token_req, block_table, k_p
     ``talk``: float32 ``[n_heads, n_heads]``, the heads' scores mixed before the softmax; ``gate``: ``[T, n_heads]``
     in the pools' dtype, head ``h``'s output times ``sigmoid(gate[t, h])``, or ``[T, n_heads * value_dim]``, a gate per
     output column.  ``softcap``: scores become ``softcap * tanh(s / softcap)`` before the softmax (0: as they are).
-    ``keep_first``: beside the window, positions ``j < keep_first`` stay visible.  ``out``: the pools' dtype or float32."""
+    ``keep_first``: beside the window, positions ``j < keep_first`` stay visible.  ``out``: the pools' dtype or float32.
+    ``v_pool`` may have fewer heads than ``k_pool`` (``Hv`` dividing ``Hkv``): key heads ``c * Hkv/Hv ..`` read value head
+    ``c`` (several score maps over the same values)."""
     _need(q, torch.float32, "attention_wide q")
     _need(k_pool, None, "attention_wide k_pool")
     _need(v_pool, k_pool.dtype, "attention_wide v_pool")
     n_pages, Hkv, page, krs = k_pool.shape
     vrs = v_pool.shape[3]
-    if v_pool.shape[:3] != k_pool.shape[:3] or not (k_pool.is_contiguous() and v_pool.is_contiguous()):
+    if not _pools_fit(k_pool, v_pool):
         raise KernelError(f"attention_wide: pools {tuple(k_pool.shape)} and {tuple(v_pool.shape)}")
     if out.dtype not in (k_pool.dtype, torch.float32) or out.shape[0] != q.shape[0]:
         raise KernelError(f"attention_wide: out {out.dtype} {tuple(out.shape)} for q {tuple(q.shape)}")
@@ -980,12 +1010,12 @@ def attention_wide(q, q_head_stride: int, positions, token_req, block_table, k_p
           _p(token_req), _p(block_table), block_table.shape[1], n_pages, page, n_heads, Hkv, key_dim, value_dim, krs, vrs,
           int(window or 0), int(chunk or 0), float(scale), _p(talk), _p(k_pool), _p(v_pool), _p(gate), ldg, _p(out),
           _rows(out, "attention_wide out"), out_head_stride, _p(rows), n, _p(status), float(softcap or 0.0),
-          int(keep_first or 0) if window else 0, gate_cols, stream)
+          int(keep_first or 0) if window else 0, gate_cols, v_pool.shape[1], stream)
 
 
 _WIDE_TC_ARGS = [c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                  c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
-                 c_int, c_void_p, c_void_p, c_int, c_float, c_int, c_int, c_void_p]
+                 c_int, c_void_p, c_void_p, c_int, c_float, c_int, c_int, c_int, c_void_p]
 
 WIDE_TC = _os.environ.get("MLXB_WIDE_TC", "1") != "0"     # 0: the kernel on the CUDA cores for bfloat16 too
 
@@ -1023,7 +1053,7 @@ def attention_wide_tiles(q, q_head_stride: int, tiles, n_tiles: int, tile_querie
     _need(v_pool, torch.bfloat16, "attention_wide_tiles v_pool")
     _need(tiles, torch.int32, "attention_wide_tiles tiles")
     n_pages, Hkv, page, krs = k_pool.shape
-    if v_pool.shape[:3] != k_pool.shape[:3] or not (k_pool.is_contiguous() and v_pool.is_contiguous()):
+    if not _pools_fit(k_pool, v_pool):
         raise KernelError(f"attention_wide_tiles: pools {tuple(k_pool.shape)} and {tuple(v_pool.shape)}")
     if out.dtype not in (torch.bfloat16, torch.float32) or out.shape[0] != q.shape[0] or tiles.numel() < 4 * n_tiles:
         raise KernelError(f"attention_wide_tiles: out {out.dtype} {tuple(out.shape)} for q {tuple(q.shape)}")
@@ -1037,7 +1067,7 @@ def attention_wide_tiles(q, q_head_stride: int, tiles, n_tiles: int, tile_querie
           block_table.shape[1], n_pages, page, n_heads, Hkv, key_dim, value_dim, krs, v_pool.shape[3], int(window or 0),
           int(chunk or 0), float(scale), _p(talk), _p(k_pool), _p(v_pool), _p(gate), ldg, _p(out),
           _rows(out, "attention_wide_tiles out"), out_head_stride, _p(status), _p(scratch), int(max_len),
-          float(softcap or 0.0), int(keep_first or 0), gate_cols, stream)
+          float(softcap or 0.0), int(keep_first or 0), gate_cols, v_pool.shape[1], stream)
 
 
 def attention_wide_step(ctx, q, q_head_stride: int, cache_k, cache_v, block_table, out, out_head_stride: int, n_heads: int,
@@ -1050,6 +1080,7 @@ def attention_wide_step(ctx, q, q_head_stride: int, cache_k, cache_v, block_tabl
     if attention_wide_tc_supported(cache_k, cache_v, n_heads, key_dim, value_dim, talk is not None):
         if (ctx.n_portion and ctx.portion_tiles is not None and q_rounded is not None and talk is None and not chunk
                 and key_dim == 64 and value_dim == 64 and out_head_stride == 64 and scale > 0
+                and cache_v.shape[1] == cache_k.shape[1]
                 and (gate is None or gate.shape[1] == n_heads * value_dim)
                 and (gate is None or (_rows(gate, "attention gate") % 8 == 0 and gate.data_ptr() % 16 == 0))
                 and out.dtype == cache_k.dtype and attention_portions_tc_supported(q_rounded, out, cache_k, cache_v)):
@@ -1079,16 +1110,16 @@ def attention_wide_step(ctx, q, q_head_stride: int, cache_k, cache_v, block_tabl
 
 _LATP_ARGS = [c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_int, c_void_p,
               c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p,
-              c_void_p]
+              c_float, c_void_p]
 
 
 def latent_prepare(proj, q_off: int, c_off: int, n_heads: int, dim: int, rot_dim: int, rank: int, norm_weight, eps: float,
                    freq, interleaved: bool, positions, token_req, block_table, pool, write: bool, q_lat,
-                   q_head_stride: int, status, stream) -> None:
+                   q_head_stride: int, status, stream, mscale: float = 1.0) -> None:
     """From ``proj [T, .]`` holding ``q`` (``n_heads`` heads of ``[dim | rot_dim]`` from ``q_off``) and the down
     projection (``rank + rot_dim`` columns from ``c_off``): the token's latent row ``[rmsnorm(c) * weight | rotated
     key part | 0..]`` into ``pool [n_pages, 1, page, row]``, and every head's rotated query part, float32, into
-    columns ``rank ..`` of its ``q_head_stride`` columns of ``q_lat``."""
+    columns ``rank ..`` of its ``q_head_stride`` columns of ``q_lat``.  ``mscale``: a factor on every cosine and sine."""
     n_pages, one, page, Dh = pool.shape
     _need(proj, pool.dtype, "latent_prepare proj")
     _need(q_lat, torch.float32, "latent_prepare q_lat")
@@ -1103,7 +1134,7 @@ def latent_prepare(proj, q_off: int, c_off: int, n_heads: int, dim: int, rot_dim
           q_off, c_off, n_heads, dim, rot_dim, rank, _p(norm_weight), float(eps), _p(freq), int(bool(interleaved)),
           _p(positions), _p(token_req), _p(block_table), block_table.shape[1], n_pages, page, Dh, _p(pool),
           int(bool(write)), _p(q_lat), _rows(q_lat, "latent_prepare q_lat"), q_head_stride, proj.shape[0], _p(status),
-          stream)
+          float(mscale), stream)
 
 
 _HEADLIN_ARGS = [c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
@@ -1247,20 +1278,49 @@ MOE_FEW_MAX_INNER = 6144     # the widest row the kernel for few slots keeps in 
 
 
 def moe_route(logits, token_req, top: int, sel_expert, sel_weight, stream, score: str = "sigmoid",
-              renormalize: bool = False) -> None:
+              renormalize: bool = False, correction=None, groups: int = 1, keep_groups: int = 1, identity: int = 0,
+              renormalize_eps: float = 0.0, weight_scale: float = 1.0) -> None:
     """Per token the ``top`` experts with the largest scores (``sigmoid`` of the float32 router logits ``[T, E]``, or
     their ``softmax``) into ``sel_expert`` int32 ``[T * top]`` and their scores into ``sel_weight`` float32
-    ``[T * top]`` (``renormalize``: divided by their sum).  Rows whose ``token_req`` is negative get expert -1."""
+    ``[T * top]`` (``renormalize``: divided by their sum plus ``renormalize_eps``), times ``weight_scale``.  Rows whose
+    ``token_req`` is negative get expert -1.  ``correction``: float32 ``[E]`` added to the scores for the choice only
+    (the weights are the scores without it).  ``groups`` > 1: the experts form that many equal groups of neighbours; a
+    group's score is its largest choice score and only experts of the ``keep_groups`` best groups can be chosen.
+    ``identity``: the last so many of the ``E`` router outputs are experts without tensors; chosen, they get -2 in
+    ``sel_expert`` (``moe_plan`` passes over them, ``moe_combine`` adds weight times input for them)."""
     _need(logits, torch.float32, "moe_route logits")
     _need(sel_expert, torch.int32, "moe_route sel_expert")
     _need(sel_weight, torch.float32, "moe_route sel_weight")
     T, E = logits.shape
     if sel_expert.numel() < T * top or sel_weight.numel() < T * top or score not in MOE_SCORES:
         raise KernelError(f"moe_route: {T} tokens, {top} of {E} experts, score {score!r}")
+    if correction is not None:
+        _need(correction, torch.float32, "moe_route correction")
+        if correction.numel() != E:
+            raise KernelError(f"moe_route: a correction of {correction.numel()} for {E} experts")
     _call("moe", "mlxb_moe_route", [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
-                                    c_void_p],
+                                    c_void_p, c_int, c_int, c_int, c_float, c_float, c_void_p],
           _p(logits), _rows(logits, "moe_route logits"), _p(token_req), T, E, int(top), MOE_SCORES[score],
-          int(bool(renormalize)), _p(sel_expert), _p(sel_weight), stream)
+          int(bool(renormalize)), _p(sel_expert), _p(sel_weight), _p(correction), int(groups), int(keep_groups),
+          E - int(identity), float(renormalize_eps), float(weight_scale), stream)
+
+
+def moe_combine(x, y, sel_expert, sel_weight, h, top: int, stream, token_req=None) -> None:
+    """``x[t] += sum_c term(t, c)`` over float32 rows, in the order of the choices: ``y[t * top + c]`` (float32, the
+    expert's weighted output) for a choice with tensors, ``sel_weight[t * top + c] * h[t]`` for an identity expert
+    (``sel_expert`` -2).  ``h``: the feed-forward's input in the run's dtype.  Rows whose ``token_req`` is negative are
+    passed over."""
+    _need(x, torch.float32, "moe_combine x")
+    _need(y, torch.float32, "moe_combine y")
+    _need(sel_expert, torch.int32, "moe_combine sel_expert")
+    _need(sel_weight, torch.float32, "moe_combine sel_weight")
+    T, D = x.shape
+    if y.shape != (T * top, D) or h.shape != (T, D) or sel_expert.numel() < T * top or sel_weight.numel() < T * top:
+        raise KernelError(f"moe_combine: x {tuple(x.shape)}, y {tuple(y.shape)}, h {tuple(h.shape)}, {top} choices")
+    _call("moe", "mlxb_moe_combine", [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                      c_void_p, c_int, c_int, c_int, c_void_p],
+          dtype_code(h.dtype), _p(x), _rows(x, "moe_combine x"), _p(y), _rows(y, "moe_combine y"), _p(sel_expert),
+          _p(sel_weight), _p(h), _rows(h, "moe_combine h"), _p(token_req), T, int(top), D, stream)
 
 
 def moe_max_tiles(n_slots: int, n_experts: int, tile_rows: int) -> int:
@@ -1280,11 +1340,16 @@ def moe_plan(sel_expert, n_slots: int, n_experts: int, tile_rows: int, sorted_sl
           _p(sel_expert), n_slots, n_experts, tile_rows, max_tiles, _p(sorted_slots), _p(tile_info), _p(n_tiles), stream)
 
 
+GATED_UNITS = {"silu": 0, "bounded": 1}     # csrc/gated_unit.cuh
+
+
 def moe_gemm(a, a_div: int, w, n_out: int, sorted_slots, tile_info, n_tiles, max_tiles: int, tile_rows: int, out, stream,
-             sel_weight=None, gated: bool = False) -> None:
+             sel_weight=None, gated: bool = False, unit: str = "silu", limit: float = 0.0) -> None:
     """``out[slot] = a[slot // a_div] @ w[expert(slot)].T`` for every slot of the plan; ``w [E, n_out, K]``.  ``gated``:
     ``w [E, 2 n_out, K]`` holds gate rows then up rows and the result is ``silu(s g) * (s u)`` with ``s`` the slot's
-    routing weight.  ``out``: ``a``'s dtype or float32, ``[n_slots, n_out]``."""
+    routing weight; with ``unit="bounded"`` it is ``s g' sigmoid(1.702 g') (u' + 1)``, ``g' = min(g, limit)``,
+    ``u' = clamp(u, -limit, limit)`` (the weight on the unit's output).  ``out``: ``a``'s dtype or float32,
+    ``[n_slots, n_out]``."""
     _need(a, None, "moe_gemm a")
     _need(w, a.dtype, "moe_gemm w")
     E, NW, K = w.shape
@@ -1295,10 +1360,12 @@ def moe_gemm(a, a_div: int, w, n_out: int, sorted_slots, tile_info, n_tiles, max
     if gated:
         _need(sel_weight, torch.float32, "moe_gemm sel_weight")
     _call("moe", "mlxb_moe_gemm", [c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p, ctypes.c_longlong, c_int, c_int,
-                                   c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p],
+                                   c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_float,
+                                   c_void_p],
           dtype_code(a.dtype), int(out.dtype == torch.float32 and a.dtype != torch.float32), int(bool(gated)), _p(a),
           _rows(a, "moe_gemm a"), int(a_div), _p(w), NW * K, n_out, K, _p(sorted_slots), _p(tile_info), _p(n_tiles),
-          int(max_tiles), int(tile_rows), _p(sel_weight), _p(out), _rows(out, "moe_gemm out"), stream)
+          int(max_tiles), int(tile_rows), _p(sel_weight), _p(out), _rows(out, "moe_gemm out"), GATED_UNITS[unit],
+          float(limit), stream)
 
 
 def moe_tc05_tile_rows() -> int:
@@ -1321,11 +1388,11 @@ def moe_gather(src, a_div: int, sorted_slots, tile_info, n_tiles, max_tiles: int
 
 
 def moe_gemm_tc05(a, w, n_out: int, sorted_slots, tile_info, n_tiles, max_tiles: int, out, status, stream,
-                  sel_weight=None, gated: bool = False) -> None:
+                  sel_weight=None, gated: bool = False, unit: str = "silu", limit: float = 0.0) -> None:
     """The experts' products over a plan of ``moe_tc05_tile_rows()``-slot tiles on the 5th-generation tensor cores.
     ``a``: bfloat16 rows IN THE PLAN'S ORDER (``moe_gather``, or the gated product's own result); ``w [E, n_out, K]``.
     ``gated``: ``w [E, 2 n_out, K]`` holds gate rows then up rows and ``out`` (bfloat16, in the plan's order) is
-    ``silu(s g) * (s u)`` with ``s`` the slot's routing weight; else ``out`` (float32) gets the product of the row at
+    ``silu(s g) * (s u)`` with ``s`` the slot's routing weight (``unit``, ``limit``: as in ``moe_gemm``); else ``out`` (float32) gets the product of the row at
     place ``i`` in row ``sorted_slots[i]``.  ``status``: receives a bit if a bounded wait in the kernel gives up."""
     _need(a, torch.bfloat16, "moe_gemm_tc05 a")
     _need(w, torch.bfloat16, "moe_gemm_tc05 w")
@@ -1337,10 +1404,11 @@ def moe_gemm_tc05(a, w, n_out: int, sorted_slots, tile_info, n_tiles, max_tiles:
     if gated:
         _need(sel_weight, torch.float32, "moe_gemm_tc05 sel_weight")
     _call("moe_tcgen05", "mlxb_moe_gemm_tc05", [c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
-                                                c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p],
+                                                c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_float,
+                                                c_void_p],
           int(bool(gated)), _p(a), _rows(a, "moe_gemm_tc05 a"), a.shape[0], _p(w), E, NW, n_out, K, _p(sorted_slots),
           _p(tile_info), _p(n_tiles), int(max_tiles), _p(sel_weight), _p(out), _rows(out, "moe_gemm_tc05 out"), _p(status),
-          stream)
+          GATED_UNITS[unit], float(limit), stream)
 
 
 # --------------------------------------------------------------------------
@@ -1358,14 +1426,16 @@ def xielu(x, out, params, stream) -> None:
           dtype_code(out.dtype), _p(x), _rows(x, "xielu x"), _p(out), _rows(out, "xielu out"), F_, T, _p(params), stream)
 
 
-def gated_unit(x, out, stream) -> None:
-    """``out[t, j] = silu(x[t, j]) * x[t, F + j]`` for ``x [T, 2F]``: the halves of a fused [gate | up] projection."""
+def gated_unit(x, out, stream, unit: str = "silu", limit: float = 0.0) -> None:
+    """``out[t, j] = silu(x[t, j]) * x[t, F + j]`` for ``x [T, 2F]``: the halves of a fused [gate | up] projection.
+    ``unit="bounded"``: ``g' sigmoid(1.702 g') (u' + 1)`` with ``g' = min(g, limit)``, ``u' = clamp(u, -limit, limit)``."""
     _need(x, out.dtype, "gated_unit x")
     T, F_ = out.shape
     if x.shape != (T, 2 * F_):
         raise KernelError(f"gated_unit: x {tuple(x.shape)} for out {tuple(out.shape)}")
-    _call("elementwise", "mlxb_gated_unit", [c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
-          dtype_code(out.dtype), _p(x), _rows(x, "gated_unit x"), _p(out), _rows(out, "gated_unit out"), F_, T, stream)
+    _call("elementwise", "mlxb_gated_unit", [c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p],
+          dtype_code(out.dtype), _p(x), _rows(x, "gated_unit x"), _p(out), _rows(out, "gated_unit out"), F_, T,
+          GATED_UNITS[unit], float(limit), stream)
 
 
 def scale_by_rows(x, index, table, first: int, out, status, stream) -> None:

@@ -58,13 +58,15 @@ class PagedKVSpec:
     lie wholly before the current run are given back.  ``value_dim``: width of a value row if it differs from
     ``head_dim``; 0: no value pool at all, values are read out of the key rows (a cache of latent rows).
     ``keep_first``: beside a window, the first so many positions of the sequence stay readable for good (their pages
-    are never given back)."""
+    are never given back).  ``value_heads``: heads of the value pool if they are fewer than the key heads (a divisor of
+    them: several key heads, each a score map of its own, then read the same value head)."""
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     chunk: Optional[int] = None
     value_dim: Optional[int] = None
     keep_first: Optional[int] = None
+    value_heads: Optional[int] = None
 
 
 @dataclass(frozen=True)

@@ -74,6 +74,29 @@ class StreamBlock(Block):
         return x
 
 
+class ParallelBlock(Block):
+    """A block over a float32 residual stream whose two sublayers read the same normed input:
+    ``h = norm_1(x); x += mixer(h) + feed_forward(h)``.  There is one norm; the feed-forward is optional.  Each
+    sublayer adds its result to the stream itself (the mixer in its last product's epilogue)."""
+    replayable = True
+
+    def __init__(self, norm_1: Norm, mixer: Mixer, feed_forward: Optional[FeedForward] = None):
+        self.norm_1, self.mixer, self.feed_forward = norm_1, mixer, feed_forward
+
+    def children(self):
+        return tuple(p for p in (self.norm_1, self.mixer, self.feed_forward) if p is not None)
+
+    def cache_spec(self):
+        return self.mixer.cache_spec()
+
+    def forward(self, ctx, x, cache):
+        h = self.norm_1.forward(ctx, x)
+        x = self.mixer.forward(ctx, h, x, cache)
+        if self.feed_forward is not None:
+            x = self.feed_forward.forward(ctx, h, x)
+        return x
+
+
 class SandwichBlock(Block):
     """A block over a float32 residual stream with a norm before AND after each sublayer:
     ``x += post_1(mixer(norm_1(x)))``, then, if the layer has a feed-forward, ``x += post_2(feed_forward(norm_2(x)))``.
@@ -143,5 +166,6 @@ class SandwichBlock(Block):
 
 
 register_part("block", "pre_norm", PreNormBlock)
+register_part("block", "parallel", ParallelBlock)
 register_part("block", "sandwich", SandwichBlock)
 register_part("block", "stream", StreamBlock)

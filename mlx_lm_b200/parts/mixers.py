@@ -17,8 +17,9 @@ from typing import List, Optional
 import torch
 
 from .. import ops
-from .base import MATRIX, VECTOR, Init, Mixer, Normed, PagedKVSpec, ParamSpec, PositionEncoding, register_part
+from .base import MATRIX, VECTOR, Init, Mixer, Normed, PagedKVSpec, ParamSpec, PositionEncoding, StateSpec, register_part
 from .linear import FusedLinear, Linear
+from .positions import rotation_frequencies
 
 
 class Attention(Mixer):
@@ -276,6 +277,11 @@ class TalkingHeadsAttention(Mixer):
       with the gate's; key/query size ``dim`` and value size ``vdim`` may differ;
     * ``rot_dims``: the first so many dimensions of every q and k head turn with the position, angle
       ``p * rot_base**(-2i/rot_dims)``, pairs ``(i, i + rot_dims/2)`` or, ``interleaved``, ``(2i, 2i+1)``;
+      ``rot_scaling`` (``factor``, ``original``, ``fast``, ``slow``) stretches the slow pairs and puts a factor on
+      cosine and sine (``parts.rotation_frequencies``);
+    * ``head_norm``: every q and k head is divided by its root mean square over ``dim`` after the rotation (eps inside
+      the root, no weight);
+    * ``out_bias``: whether ``<name>.o`` has a bias (default: as the other projections);
     * ``value_norm``: every value head is divided by its root mean square (eps inside the root, no weight)
       before it enters the cache;
     * ``talk``: the heads' scores ``scale * q_g . k`` are mixed before the softmax, ``s_h <- sum_g T[h, g] s_g``
@@ -303,11 +309,15 @@ class TalkingHeadsAttention(Mixer):
                  talk: bool = True, value_norm: bool = True, head_gate: bool = True, window: Optional[int] = None,
                  chunk: Optional[int] = None, init: Init = Init(), bias_init: Init = Init(), column_gate: bool = False,
                  softcap: float = 0.0, keep_first: int = 0, own_kv: bool = True, cache_window: Optional[int] = None,
-                 cache_keep_first: Optional[int] = None):
+                 cache_keep_first: Optional[int] = None, rot_scaling: Optional[dict] = None, head_norm: bool = False,
+                 out_bias: Optional[bool] = None):
         if n_heads % n_kv_heads:
             raise ValueError(f"{name}: {n_heads} query heads are not a multiple of {n_kv_heads} key/value heads")
         if rot_dims % 2 or rot_dims > dim:
             raise ValueError(f"{name}: {rot_dims} rotated dimensions of {dim}")
+        if not own_kv and head_norm:
+            raise ValueError(f"{name}: a layer that reads another layer's pages does not norm their keys")
+        self.rot_scaling, self.head_norm, self.rot_mscale = rot_scaling, head_norm, 1.0
         if head_gate and column_gate:
             raise ValueError(f"{name}: a gate per head or a gate per column, not both")
         if keep_first and not window:
@@ -332,6 +342,7 @@ class TalkingHeadsAttention(Mixer):
         self.proj = FusedLinear(f"{name}.qkvg", width, sources, init=init, biases=biases, bias_init=bias_init)
         self.out = Linear(f"{name}.o", n_heads * vdim, width, bias=False, weight_suffix="", init=init)
         self.has_bias, self.bias_init = bias, bias_init
+        self.has_out_bias = bias if out_bias is None else bool(out_bias)
         self.talk = self.freq = None
         if dim == 64 and vdim == 64 and not rot_dims and not talk and not chunk and not head_gate:
             # plain heads of 64: prompt portions run on the tcgen05 kernel
@@ -348,7 +359,7 @@ class TalkingHeadsAttention(Mixer):
         specs = []
         if self.has_talk:
             specs.append(ParamSpec(f"{self.name}.talk", (self.n_heads, self.n_heads), VECTOR, Init(0.0, 0.5)))
-        if self.has_bias:
+        if self.has_out_bias:
             specs.append(ParamSpec(f"{self.name}.o.b", (self.width,), VECTOR, self.bias_init))
         return specs
 
@@ -356,12 +367,12 @@ class TalkingHeadsAttention(Mixer):
         if self.has_talk:
             self.talk = tensors[f"{self.name}.talk"].contiguous()
         if self.rot_dims:
-            i = torch.arange(self.rot_dims // 2, dtype=torch.float64)
-            self.freq = (self.rot_base ** (-2.0 * i / self.rot_dims)).to(torch.float32).to(device)
+            f, self.rot_mscale = rotation_frequencies(self.rot_dims, self.rot_base, self.rot_scaling)
+            self.freq = torch.tensor(f, dtype=torch.float64).to(torch.float32).to(device)
 
     def bind_all(self, tensors, dtype, device) -> None:
         super().bind_all(tensors, dtype, device)
-        if self.has_bias:
+        if self.has_out_bias:
             self.out.bias = tensors[f"{self.name}.o.b"]     # named beside the tensor, not ".bias": set once the layer is bound
 
     def forward(self, ctx, x, residual, cache):
@@ -391,8 +402,8 @@ class TalkingHeadsAttention(Mixer):
         if self.head_gate or self.column_gate:
             g_off = self.proj.offset(f"{self.name}.g")
             gate = proj[:, g_off:g_off + (H * self.vdim if self.column_gate else H)]
-        # without a rotation the product's own (rounded) query columns are the queries
-        q_rounded = proj[:, :H * self.dim] if not self.rot_dims and proj.dtype == cache.k.dtype else None
+        # without a rotation (and without a norm of the heads) the product's own (rounded) query columns are the queries
+        q_rounded = proj[:, :H * self.dim] if not self.rot_dims and not self.head_norm and proj.dtype == cache.k.dtype else None
         ops.attention_wide_step(ctx, q, self.key_row, cache.k, cache.v, cache.block_table, o, self.vdim, H, self.dim,
                                 self.vdim, self.scale, window=self.window or 0, chunk=self.chunk or 0, talk=self.talk,
                                 gate=gate, softcap=self.softcap, keep_first=self.keep_first, q_rounded=q_rounded)
@@ -404,7 +415,8 @@ class TalkingHeadsAttention(Mixer):
         ops.qkv_prepare(proj, 0, H * self.dim, (H + G) * self.dim, H, G, self.dim, self.vdim, None, None, self.eps,
                         self.freq, ctx.positions, ctx.token_req, cache.block_table, cache.k, cache.v, q, cache.write,
                         ctx.status, ctx.stream, interleaved=self.interleaved,
-                        v_norm_eps=self.eps if self.value_norm else None)
+                        v_norm_eps=self.eps if self.value_norm else None, mscale=self.rot_mscale,
+                        head_norm_eps=self.eps if self.head_norm else None)
 
 
 class LatentAttention(Mixer):
@@ -420,15 +432,18 @@ class LatentAttention(Mixer):
     rows with all heads sharing them (the values are the rows' first ``kv_rank`` columns), and the values'
     up-projection is applied to its output (again a product per head), then ``<name>.o``.  Queries and the
     attention's output stay float32 between those products.  Rotation pairs ``(2i, 2i+1)`` (``interleaved``) or
-    ``(i, i + rot_dim/2)``; ``window`` as in the other attention parts."""
+    ``(i, i + rot_dim/2)``, optionally stretched (``rot_scaling``, see ``parts.rotation_frequencies``; the scores' scale
+    stays as given); ``window`` as in the other attention parts."""
     replayable = True
     kernel_libs = ("attention_wide", "attention_wide_tc", "latent")
 
     def __init__(self, name: str, width: int, n_heads: int, dim: int, rot_dim: int, vdim: int, kv_rank: int,
                  scale: float, eps: float, rot_base: float = 10000.0, interleaved: bool = True,
-                 window: Optional[int] = None, chunk: Optional[int] = None, init: Init = Init()):
+                 window: Optional[int] = None, chunk: Optional[int] = None, init: Init = Init(),
+                 rot_scaling: Optional[dict] = None):
         if rot_dim % 2:
             raise ValueError(f"{name}: {rot_dim} rotated dimensions")
+        self.rot_scaling, self.rot_mscale = rot_scaling, 1.0
         self.name, self.width = name, width
         self.n_heads, self.dim, self.rot_dim, self.vdim, self.rank = n_heads, dim, rot_dim, vdim, kv_rank
         self.scale, self.eps, self.window, self.chunk = float(scale), float(eps), window, chunk
@@ -462,8 +477,8 @@ class LatentAttention(Mixer):
         self.w_absorb = tensors[f"{n}.uk"].view(H, self.dim, R).transpose(1, 2).contiguous()
         self.w_values = tensors[f"{n}.uv"].view(H, self.vdim, R).contiguous()
         if self.rot_dim:
-            i = torch.arange(self.rot_dim // 2, dtype=torch.float64)
-            self.freq = (self.rot_base ** (-2.0 * i / self.rot_dim)).to(torch.float32).to(device)
+            f, self.rot_mscale = rotation_frequencies(self.rot_dim, self.rot_base, self.rot_scaling)
+            self.freq = torch.tensor(f, dtype=torch.float64).to(torch.float32).to(device)
 
     def forward(self, ctx, x, residual, cache):
         T, H, R = x.shape[0], self.n_heads, self.rank
@@ -474,7 +489,7 @@ class LatentAttention(Mixer):
         ops.label(self.name + ".prepare", 8.0 * T * n, x.element_size() * T * (n + self.row) + 4.0 * T * H * self.rot_dim)
         ops.latent_prepare(proj, 0, H * self.q_head, H, self.dim, self.rot_dim, R, self.norm_w, self.eps, self.freq,
                            self.interleaved, ctx.positions, ctx.token_req, cache.block_table, cache.k, cache.write, q_lat,
-                           self.lat, ctx.status, ctx.stream)
+                           self.lat, ctx.status, ctx.stream, mscale=self.rot_mscale)
         ops.label(self.name + ".uk", 2.0 * T * H * self.dim * R, x.element_size() * (T * H * self.dim + H * self.dim * R)
                   + 4.0 * T * H * R)
         ops.head_linear(proj, self.q_head, self.w_absorb, q_lat, self.lat, ctx.stream, token_req=ctx.token_req)
@@ -492,7 +507,132 @@ class LatentAttention(Mixer):
         return self.out.forward(ctx, o, residual, residual=residual)
 
 
+class DifferentialAttention(Mixer):
+    """Grouped-query causal attention with two score maps per head over the same values.
+
+    ``<name>.q`` gives every query head ``[map 1 | map 2]`` (``2 * dim`` columns), ``<name>.k`` every key head the
+    same, ``<name>.v`` every key/value head ``vdim`` columns; no biases, no rotation.  With ``taps`` > 0 each channel
+    of q, k and v passes a short causal convolution over time right after the projection (``<tensor>.conv``
+    ``[channels, taps]``, last column: the current token; no bias, no activation) whose last ``taps - 1`` inputs are
+    part of the request's state.  Each map is an ordinary softmax attention ``a_m`` with scores ``scale * q_m . k_m``;
+    a head's output is ``o = a_1 - lambda a_2`` with one number for the layer,
+    ``lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + diff`` (``<name>.lq1`` and so on, ``dim`` values each), then ``o``
+    divided by its root mean square over ``vdim`` (eps inside the root, no weight) and multiplied by ``1 - diff``,
+    then ``<name>.o``.
+
+    The pages hold ``2 * kv_heads`` key heads (a key head's two maps side by side) and ``kv_heads`` value heads
+    (``PagedKVSpec.value_heads``); the attention kernels run ``2 * heads`` independent query heads, ordered (when the
+    weights are bound, by a permutation of the rows of ``q`` and of its convolution) so that the queries of one key
+    head lie together: group ``g`` holds ``[map 1 of its heads | map 2 of its heads]``."""
+    replayable = True
+    kernel_libs = ("attention_wide", "attention_wide_tc", "rotary", "recurrent", "rms")
+
+    def __init__(self, name: str, width: int, n_heads: int, n_kv_heads: int, dim: int, vdim: int, scale: float,
+                 eps: float, diff: float, taps: int = 0, init: Init = Init()):
+        if n_heads % n_kv_heads:
+            raise ValueError(f"{name}: {n_heads} query heads are not a multiple of {n_kv_heads} key/value heads")
+        if taps < 0 or taps > 9:
+            raise ValueError(f"{name}: a convolution of {taps} taps (at most 9)")
+        self.name, self.width = name, width
+        self.n_heads, self.n_kv_heads, self.dim, self.vdim = n_heads, n_kv_heads, dim, vdim
+        self.scale, self.eps, self.diff, self.taps = float(scale), float(eps), float(diff), int(taps or 0)
+        self.key_row, self.value_row = (dim + 7) // 8 * 8, (vdim + 7) // 8 * 8
+        self.q_width, self.k_width, self.v_width = n_heads * 2 * dim, n_kv_heads * 2 * dim, n_kv_heads * vdim
+        self.conv_width = self.q_width + self.k_width + self.v_width
+        self.proj = FusedLinear(f"{name}.qkv", width, [(f"{name}.q", self.q_width), (f"{name}.k", self.k_width),
+                                                       (f"{name}.v", self.v_width)], init=init)
+        self.out = Linear(f"{name}.o", n_heads * vdim, width, bias=False, weight_suffix="", init=init)
+        self.lam = 0.0
+        self.conv_w = self.conv_wt = self._no_state = None
+
+    def children(self):
+        return (self.proj, self.out)
+
+    def cache_spec(self):
+        kv = PagedKVSpec(2 * self.n_kv_heads, self.key_row, None, value_dim=self.value_row, value_heads=self.n_kv_heads)
+        if self.taps > 1:
+            return {"kv": kv, "conv": StateSpec((self.taps - 1, self.conv_width))}
+        return kv
+
+    def param_specs(self) -> List[ParamSpec]:
+        n = self.name
+        specs = []
+        if self.taps:
+            specs += [ParamSpec(f"{n}.{t}.conv", (w, self.taps), VECTOR, Init(0.0, 0.4))
+                      for t, w in (("q", self.q_width), ("k", self.k_width), ("v", self.v_width))]
+        specs += [ParamSpec(f"{n}.{t}", (self.dim,), VECTOR, Init(0.0, 0.1)) for t in ("lq1", "lk1", "lq2", "lk2")]
+        return specs
+
+    def _query_order(self, device) -> torch.Tensor:
+        """Rows of the stored ``q`` in the order the kernels want them: blocks of ``dim`` rows, block ``(g, m, r)`` (key
+        head, map, query head of the group) taken from the stored block ``(g * rep + r, m)``."""
+        H, G, d = self.n_heads, self.n_kv_heads, self.dim
+        rep = H // G
+        blocks = [(g * rep + r) * 2 + m for g in range(G) for m in range(2) for r in range(rep)]
+        idx = torch.tensor(blocks, dtype=torch.long, device=device)[:, None] * d + torch.arange(d, device=device)[None, :]
+        return idx.reshape(-1)
+
+    def bind(self, tensors, dtype, device) -> None:
+        n = self.name
+        f = lambda t: tensors[f"{n}.{t}"].float()
+        self.lam = float(torch.exp((f("lq1") * f("lk1")).sum()) - torch.exp((f("lq2") * f("lk2")).sum())) + self.diff
+        order = self._query_order(device)
+        if self.taps:
+            self.conv_w = torch.cat([tensors[f"{n}.q.conv"][order], tensors[f"{n}.k.conv"], tensors[f"{n}.v.conv"]],
+                                    dim=0).contiguous()
+            self.conv_wt = self.conv_w.t().contiguous()
+            self._no_state = torch.zeros((1, 0, self.conv_width), dtype=torch.float32, device=device)
+
+    def bind_all(self, tensors, dtype, device) -> None:
+        super().bind_all(tensors, dtype, device)
+        w = self.proj.weight
+        self.proj.use_weight(torch.cat([w[:self.q_width][self._query_order(w.device)], w[self.q_width:]], dim=0).contiguous())
+
+    def forward(self, ctx, x, residual, cache):
+        return self.out.forward(ctx, self._heads_out(ctx, x, cache), residual, residual=residual)
+
+    def mix(self, ctx, x, cache, tag: str = "mix_out"):
+        o = self._heads_out(ctx, x, cache)
+        return self.out.forward(ctx, o, ctx.ws.get(tag, x.shape[0], self.width, torch.float32))
+
+    def _heads_out(self, ctx, x, cache):
+        T, H, G, C = x.shape[0], self.n_heads, self.n_kv_heads, self.conv_width
+        kv = cache.side("kv") if self.taps > 1 else cache
+        es = x.element_size()
+        qkv = ctx.ws.get("attn_proj", T, (C + 7) // 8 * 8, x.dtype)[:, :C]
+        self.proj.forward(ctx, x, qkv)
+        if self.taps:
+            conv = ctx.ws.get("attn_conv", T, (C + 7) // 8 * 8, x.dtype)[:, :C]
+            ops.label(self.name + ".conv", 2.0 * self.taps * T * C, 2.0 * es * T * C)
+            if self.taps > 1:
+                st = cache.side("conv")
+                state, slots = st.state, st.slots
+            else:
+                state, slots = self._no_state, ctx._slots
+            ops.conv_silu(qkv, self.conv_w, None, state, slots, ctx.positions, ctx.token_req, ctx.req_first_token,
+                          ctx.req_first_position, conv, ctx.stream, weight_by_tap=self.conv_wt, activation=False)
+            qkv = conv
+        q = ctx.ws.get("attn_q32", T, 2 * H * self.key_row, torch.float32)
+        ops.label(self.name + ".prepare", 2.0 * T * C, (es + 4.0) * T * C)
+        ops.qkv_prepare(qkv, 0, self.q_width, self.q_width + self.k_width, 2 * H, 2 * G, self.dim, self.vdim, None, None,
+                        self.eps, None, ctx.positions, ctx.token_req, kv.block_table, kv.k, kv.v, q, kv.write, ctx.status,
+                        ctx.stream)
+        maps = ctx.ws.get("attn_maps", T, 2 * H * self.vdim, torch.float32)
+        if ops.recording():
+            pairs, keys = visible_pairs(ctx, None, None)
+            ops.label(self.name + ".attention", pairs * 2 * H * (2.0 * self.dim + 2.0 * self.vdim),
+                      es * keys * G * (2 * self.key_row + self.value_row) + 4.0 * T * 2 * H * (self.dim + self.vdim))
+        ops.attention_wide_step(ctx, q, self.key_row, kv.k, kv.v, kv.block_table, maps, self.vdim, 2 * H, self.dim,
+                                self.vdim, self.scale)
+        o = ctx.ws.get("attn_out", T, H * self.vdim, x.dtype)
+        ops.label(self.name + ".difference", 6.0 * T * H * self.vdim, (8.0 + es) * T * H * self.vdim)
+        ops.head_difference(maps, H // G, self.vdim, self.lam, self.eps, 1.0 - self.diff, o, ctx.stream,
+                            token_req=ctx.token_req)
+        return o
+
+
 register_part("mixer", "sink_attention", SinkAttention)
+register_part("mixer", "differential_attention", DifferentialAttention)
 register_part("mixer", "talking_heads_attention", TalkingHeadsAttention)
 register_part("mixer", "latent_attention", LatentAttention)
 register_part("mixer", "parallel", ParallelMixer)

@@ -58,6 +58,33 @@ class Sinusoidal(PositionEncoding):
         return self.freq
 
 
+def rotation_frequencies(dims: int, base: float, scaling: Optional[dict] = None):
+    """``(frequencies, factor)`` of a rotation of ``dims`` dimensions: pair ``i`` turns by ``p * f_i`` with
+    ``f_i = base**(-2i / dims)`` (float64 list), cosine and sine both times ``factor``.  ``scaling`` (``factor``,
+    ``original``, ``fast``, ``slow``) stretches the slow pairs for sequences longer than ``original`` positions: with
+    ``d(t) = dims * ln(original / (2 pi t)) / (2 ln base)`` (the pair that makes ``t`` turns over ``original``
+    positions), ``lo = max(floor(d(fast)), 0)``, ``hi = min(ceil(d(slow)), dims - 1)`` and
+    ``ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1)``, the frequency becomes
+    ``f_i / factor * ramp_i + f_i * (1 - ramp_i)`` and cosine and sine are multiplied by ``0.1 ln(factor) + 1``."""
+    import math
+
+    f = [float(base) ** (-2.0 * i / dims) for i in range(dims // 2)]
+    if not scaling:
+        return f, 1.0
+    factor, original = float(scaling["factor"]), float(scaling["original"])
+
+    def pair_of(turns: float) -> float:
+        return dims * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(float(base)))
+
+    lo = max(math.floor(pair_of(float(scaling["fast"]))), 0)
+    hi = min(math.ceil(pair_of(float(scaling["slow"]))), dims - 1)
+    out = []
+    for i, fi in enumerate(f):
+        ramp = min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0)
+        out.append(fi / factor * ramp + fi * (1.0 - ramp))
+    return out, 0.1 * math.log(factor) + 1.0
+
+
 register_part("position", "learned_absolute", LearnedAbsolute)
 register_part("position", "sinusoidal", Sinusoidal)
 register_part("position", "none", NoPosition)
