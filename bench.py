@@ -705,6 +705,45 @@ def dalorax_config(width, vocab):
             "layers": layers}
 
 
+def zuluvik_config(width, vocab):
+    """Ten layer runs of the sizes a model of this width would have: latent rows of 256 + 32 columns; attention with
+    two score maps per head (half as many heads, maps of 64, values of 128, a quarter as many key/value heads,
+    convolutions of four taps); rotated attention with heads of 64 normed after a stretched rotation; on every layer
+    fourteen experts and two identity experts in four groups of which two stay, two a token, of a quarter of a dense
+    feed-forward's inner size, and a shared expert of that size.  One layer runs an earlier layer's weights again."""
+    H = width // 64
+    inner = (width * 11 // 4 + 127) // 128 * 128
+    stretch = {"factor": 8.0, "original": 1024, "fast": 32.0, "slow": 1.0}
+    moe = {"kind": "moe", "expert": {"ff": inner // 4, "limit": 7.0},
+           "router": {"experts": 14, "identity": 2, "top": 2, "scale": 1.5, "groups": {"count": 4, "keep": 2}},
+           "shared": {"ff": inner // 4, "limit": 7.0}}
+    lat = {"type": "latent_attention", "mlp": moe,
+           "mixer": {"dim": 64, "heads": H, "kv_rank": 256, "rot_dim": 32, "vdim": 64, "scale": 0.1,
+                     "rot": {"base": 500000.0, "dims": 32, "scaling": stretch}}}
+    two = {"type": "attention", "mlp": moe,
+           "mixer": {"dim": 64, "heads": max(1, H // 2), "kv_heads": max(1, H // 8), "vdim": 128, "scale": 0.125, "diff": 0.3,
+                     "conv": 4}}
+    rot = {"type": "attention_2", "mlp": moe,
+           "mixer": {"dim": 64, "heads": H, "kv_heads": max(1, H // 4), "vdim": 64, "scale": 0.125,
+                     "rot": {"base": 500000.0, "dims": 64, "scaling": stretch}}}
+    layers = [lat, two, rot, rot, lat, dict(two, weights_of=1), rot, lat, two, rot]
+    return {"architecture": "Zuluvik", "vocab": vocab, "width": width, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-5},
+            "layers": layers}
+
+
+def run_zuluvik(args):
+    """The same measurements as ``--only dalorax`` for the Zuluvik design, beside Dalorax (the nearest design in the
+    tree: a float32 stream, grouped-query attention over pages and mixtures of experts) and Nufetar (attention over
+    latent rows and rotated attention on the same kernels) at equal width and as many layer runs."""
+    vocab = 32000
+
+    def models(width):
+        zul = zuluvik_config(width, vocab)
+        return len(zul["layers"]), [("zuluvik", zul), ("dalorax", dalorax_config(width, vocab)),
+                                    ("nufetar", nufetar_config(width, vocab))]
+    run_beside(args, "zuluvik_vs_dalorax", models)
+
+
 def run_dalorax(args):
     """The same measurements as ``--only nufetar`` for the Dalorax design, beside Nufetar (the nearest design in the
     tree: a float32 stream, the same windowed attention part, gated feed-forwards) at equal width and as many layers."""
@@ -826,9 +865,9 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration's 24 (0 = all)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--widths", default="", help="with --only lelatar / nufetar / dalorax: the model widths to run, with commas (default 1024,2048)")
+    ap.add_argument("--widths", default="", help="with --only lelatar / nufetar / dalorax / zuluvik: the model widths to run, with commas (default 1024,2048)")
     ap.add_argument("--only", default="", choices=["", "decode", "prefill", "mixed", "timeline", "kernels", "yardstick",
-                                                   "lelatar", "nufetar", "dalorax"],
+                                                   "lelatar", "nufetar", "dalorax", "zuluvik"],
                     help="run just this part and print its figures (decode / prefill: short runs for profiling; "
                          "mixed: 64 requests with prompts of 16..1024 tokens through the scheduler, 256-token portions "
                          "beside decoding requests; timeline: every kernel of one step with its start and end, "
@@ -837,7 +876,7 @@ def main():
                          "model's linear shapes, to hold the hand-written kernels against; lelatar: prefill and decode of "
                          "the Lelatar design at two widths beside GPT-2 of equal width and layer runs, with every kernel "
                          "of both against its roofline; nufetar: the same for the Nufetar design beside Lelatar; dalorax: the same for the Dalorax design "
-                         "beside Nufetar)")
+                         "beside Nufetar; zuluvik: the same for the Zuluvik design beside Dalorax and Nufetar)")
     ap.add_argument("--prefill-prompts", type=int, default=0,
                     help="with --only prefill: 1024-token prompts in the one step (default and the contract's figure: "
                          "2); with --only timeline: the timeline of such a step instead of a decode step")
@@ -861,6 +900,9 @@ def main():
         return 0
     if a.only == "dalorax":
         run_dalorax(a)
+        return 0
+    if a.only == "zuluvik":
+        run_zuluvik(a)
         return 0
     run_ours(a)
     return 0

@@ -344,9 +344,10 @@ class TalkingHeadsAttention(Mixer):
         self.has_bias, self.bias_init = bias, bias_init
         self.has_out_bias = bias if out_bias is None else bool(out_bias)
         self.talk = self.freq = None
-        if dim == 64 and vdim == 64 and not rot_dims and not talk and not chunk and not head_gate:
-            # plain heads of 64: prompt portions run on the tcgen05 kernel
-            self.kernel_libs = type(self).kernel_libs + ("attention_prefill_tc",)
+        if dim == 64 and vdim == 64 and not talk and not chunk and not head_gate:
+            # plain heads of 64: prompt portions run on the tcgen05 kernel (queries that were turned or normed reach it
+            # through a bfloat16 copy)
+            self.kernel_libs = type(self).kernel_libs + ("attention_prefill_tc", "elementwise")
 
     def children(self):
         return (self.proj, self.out)
@@ -393,6 +394,14 @@ class TalkingHeadsAttention(Mixer):
         q = ctx.ws.get("attn_q32", T, H * self.key_row, torch.float32)
         ops.label(self.name + ".prepare", 8.0 * T * n, (x.element_size() + 4.0) * T * n)
         self._prepare(ctx, proj, cache, q)
+        # without a rotation (and without a norm of the heads) the product's own (rounded) query columns are the queries
+        q_rounded = proj[:, :H * self.dim] if not self.rot_dims and not self.head_norm and proj.dtype == cache.k.dtype else None
+        if (q_rounded is None and ctx.n_portion and ctx.portion_tiles is not None and "attention_prefill_tc" in self.kernel_libs
+                and proj.dtype == torch.bfloat16 and cache.k.dtype == torch.bfloat16 and ops.PREFILL_TC):
+            # turned or normed queries of plain heads of 64: the tcgen05 kernel for portions takes them in bfloat16
+            q_rounded = ctx.ws.get("attn_q16", T, H * self.key_row, torch.bfloat16)
+            ops.label(self.name + ".prepare.cast", 0.0, 6.0 * T * H * self.key_row)
+            ops.join_rows(q, None, q_rounded, ctx.stream)
         o = ctx.ws.get("attn_out", T, H * self.vdim, x.dtype)
         if ops.recording():
             pairs, keys = visible_pairs(ctx, self.window, self.chunk)
@@ -402,8 +411,6 @@ class TalkingHeadsAttention(Mixer):
         if self.head_gate or self.column_gate:
             g_off = self.proj.offset(f"{self.name}.g")
             gate = proj[:, g_off:g_off + (H * self.vdim if self.column_gate else H)]
-        # without a rotation (and without a norm of the heads) the product's own (rounded) query columns are the queries
-        q_rounded = proj[:, :H * self.dim] if not self.rot_dims and not self.head_norm and proj.dtype == cache.k.dtype else None
         ops.attention_wide_step(ctx, q, self.key_row, cache.k, cache.v, cache.block_table, o, self.vdim, H, self.dim,
                                 self.vdim, self.scale, window=self.window or 0, chunk=self.chunk or 0, talk=self.talk,
                                 gate=gate, softcap=self.softcap, keep_first=self.keep_first, q_rounded=q_rounded)
