@@ -627,7 +627,7 @@ class DifferentialAttention(Mixer):
         maps = ctx.ws.get("attn_maps", T, 2 * H * self.vdim, torch.float32)
         if ops.recording():
             pairs, keys = visible_pairs(ctx, None, None)
-            ops.label(self.name + ".attention", pairs * 2 * H * (2.0 * self.dim + 2.0 * self.vdim),
+            ops.label(self.name + ".maps.attention", pairs * 2 * H * (2.0 * self.dim + 2.0 * self.vdim),
                       es * keys * G * (2 * self.key_row + self.value_row) + 4.0 * T * 2 * H * (self.dim + self.vdim))
         ops.attention_wide_step(ctx, q, self.key_row, kv.k, kv.v, kv.block_table, maps, self.vdim, 2 * H, self.dim,
                                 self.vdim, self.scale)
