@@ -27,6 +27,7 @@
 // page of the tile's first query instead: their scores are masked, and the values they are multiplied with (by zero)
 // must be finite.
 //
+// Values may have fewer heads than the keys and rows of several 64-column slices (grid.y = head x slice).
 // Options of newer designs, each an argument: `softcap` (scores become softcap * tanh(scale * s / softcap) before the
 // softmax), `keep_first` (beside a window the first so many positions of the sequence stay visible: their blocks are
 // walked first, then the window's), `gate` (every output column times the sigmoid of a bfloat16 gate column).
@@ -147,7 +148,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             const int* __restrict__ block_table, int max_pages, int n_pages, int page, int Hq, int Hkv,
                             int window, float scale_log2e, __nv_bfloat16* out, int ldo, int* __restrict__ status,
                             const float* __restrict__ sinks, int keep_first, float softcap,
-                            const __nv_bfloat16* gate, int ldg) {
+                            const __nv_bfloat16* gate, int ldg, int Hv, int VS, int out_f32) {
   extern __shared__ uint8_t smem_raw[];
   AtSmem& sm = *reinterpret_cast<AtSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -182,7 +183,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 
   const int4 tile = tiles[blockIdx.x];
   const int row0 = tile.x, n_rows = tile.y, req = tile.z, pos0 = tile.w;
-  const int h = blockIdx.y, hk = h / (Hq / Hkv);
+  // grid.y = query head x slice of 64 value columns (VS slices of a value row; one where values are 64 wide)
+  const int h = blockIdx.y / VS, vs = blockIdx.y - h * VS, hk = h / (Hq / Hkv), hv = hk / (Hkv / Hv);
   const int last_pos = pos0 + n_rows - 1;
   const int first_key = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
   const int kb_lo = first_key / TK, kb_hi = last_pos / TK;
@@ -219,18 +221,19 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       }
       return pg;
     };
-    auto load_pages = [&](const CUtensorMap* map, __nv_bfloat16* dst, uint64_t* bar, int pg) {
+    // (keys: head hk of Hkv, column 0; values: head hv of Hv, the slice's 64 columns)
+    auto load_pages = [&](const CUtensorMap* map, __nv_bfloat16* dst, uint64_t* bar, int pg, int heads, int head, int x) {
       if (lane == 0) mbar_expect_tx(bar, TK * HD * (uint32_t)sizeof(__nv_bfloat16));
       __syncwarp();
-      if (lane < pages_per_block) tma_load_2d(dst + (size_t)lane * page * HD, map, 0, (pg * Hkv + hk) * page, bar);
+      if (lane < pages_per_block) tma_load_2d(dst + (size_t)lane * page * HD, map, x, (pg * heads + head) * page, bar);
     };
     int pg_now = page_of(kb_at(0));
     if (lane == 0) {
       mbar_expect_tx(&sm.q_full, TQ * HD * (uint32_t)sizeof(__nv_bfloat16));
       tma_load_2d(sm.q, &map_q, h * HD, row0, &sm.q_full);
     }
-    load_pages(&map_k, sm.k, &sm.k_full, pg_now);
-    load_pages(&map_v, sm.v, &sm.v_full, pg_now);
+    load_pages(&map_k, sm.k, &sm.k_full, pg_now, Hkv, hk, 0);
+    load_pages(&map_v, sm.v, &sm.v_full, pg_now, Hv, hv, vs * HD);
     int pg_next = page_of(kb_at(1));
 
     constexpr uint32_t idesc_s = umma_idesc(TQ, TK, false);
@@ -257,7 +260,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       const uint32_t ph = (uint32_t)(i & 1);
       const bool more = i + 1 < n_blocks;
       if (!(ok = mbar_wait_warp(&sm.s_full, ph, abort_flag))) break;    // S(i) is there: the K block is free
-      if (more) load_pages(&map_k, sm.k, &sm.k_full, pg_next);
+      if (more) load_pages(&map_k, sm.k, &sm.k_full, pg_next, Hkv, hk, 0);
       if (!(ok = mbar_wait_warp(&sm.v_full, ph, abort_flag))) break;
       if (!(ok = mbar_wait_warp(&sm.p_full, ph, abort_flag))) break;    // P(i) is written, S(i) has been read
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -279,7 +282,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       }
       const int pg_after = page_of(kb_at(i + 2));                 // its latency hides behind the wait below
       if (!(ok = mbar_wait_warp(&sm.o_full, ph, abort_flag))) break;    // O_b(i) is there: V and P are free
-      if (more) load_pages(&map_v, sm.v, &sm.v_full, pg_next);
+      if (more) load_pages(&map_v, sm.v, &sm.v_full, pg_next, Hv, hv, vs * HD);
       pg_next = pg_after;
     }
   } else {
@@ -391,7 +394,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     if (ok && r < n_rows) {
       if (sinks && m != -INFINITY) l += fast_exp2(sinks[h] * 1.4426950408889634f - m);   // the sink: no key, no value
       const float inv = l > 0.f ? 1.f / l : 0.f;
-      __nv_bfloat16* dst = out + (size_t)(row0 + r) * ldo + h * HD + half * (HD / 2);
+      const size_t col = (size_t)(h * VS + vs) * HD + half * (HD / 2);      // this thread's first output column
+      __nv_bfloat16* dst = out + (size_t)(row0 + r) * ldo + col;
+      float* dst32 = reinterpret_cast<float*>(out) + (size_t)(row0 + r) * ldo + col;
 #pragma unroll
       for (int d = 0; d < HD / 2; d += 8) {
         float v8[8];
@@ -399,11 +404,16 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         for (int e = 0; e < 8; ++e) v8[e] = o[d + e] * inv;
         if (gate) {
           float g8[8];
-          unpack8(*reinterpret_cast<const uint4*>(gate + (size_t)(row0 + r) * ldg + h * HD + half * (HD / 2) + d), g8);
+          unpack8(*reinterpret_cast<const uint4*>(gate + (size_t)(row0 + r) * ldg + col + d), g8);
 #pragma unroll
           for (int e = 0; e < 8; ++e) v8[e] *= 1.f / (1.f + expf(-g8[e]));
         }
-        *reinterpret_cast<uint4*>(dst + d) = pack8(v8);
+        if (out_f32) {
+          *reinterpret_cast<float4*>(dst32 + d) = make_float4(v8[0], v8[1], v8[2], v8[3]);
+          *reinterpret_cast<float4*>(dst32 + d + 4) = make_float4(v8[4], v8[5], v8[6], v8[7]);
+        } else {
+          *reinterpret_cast<uint4*>(dst + d) = pack8(v8);
+        }
       }
     }
   }
@@ -439,13 +449,21 @@ static int make_map(CUtensorMap* map, const void* base, long long rows, int cols
 // bfloat16, heads of 64.  q: [n_tokens, >= Hq*64] at row stride ldq (a multiple of 8, base 16-byte aligned);
 // out: [*, Hq*64] at row stride ldo (a multiple of 8, 16-byte aligned); tiles: int32 [n_tiles][4], see the kernel
 // (tiles of at most 128 queries; a tile of 0 queries is skipped); pools [n_pages, Hkv, page, 64], page a power of two from 8 to 128.
+// Hv, Dv (0: Hkv, 64): the value pool is [n_pages, Hv, page, Dv] with Hv a divisor of Hkv (key heads c * Hkv/Hv .. read
+// value head c: several score maps over the same values) and Dv a multiple of 64; a CTA then takes one slice of 64
+// value columns (the scores are formed once per slice) and out is [*, Hq*Dv].  out_f32: out is float32.
 MLXB_EXPORT int mlxb_attention_prefill_tc(const void* q, int ldq, int n_tokens, const int* tiles, int n_tiles,
                                           const int* block_table, int max_pages, int n_pages, int page, int Hq,
                                           int Hkv, int Dh, int window, float scale, const void* k_pool,
                                           const void* v_pool, void* out, int ldo, int* status, const float* sinks,
-                                          int keep_first, float softcap, const void* gate, int ldg,
-                                          cudaStream_t stream) {
+                                          int keep_first, float softcap, const void* gate, int ldg, int Hv, int Dv,
+                                          int out_f32, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
+  if (Hv <= 0) Hv = Hkv;
+  if (Dv <= 0) Dv = HD;
+  if (Hkv <= 0 || Hkv % Hv || Dv % HD || (long long)Hq * (Dv / HD) > 65535)
+    return mlxb_fail(MLXB_BAD_ARG, "attention (portions, tcgen05): %d key heads over %d value heads of %d columns", Hkv, Hv, Dv);
+  const int VS = Dv / HD;
   if (keep_first < 0 || softcap < 0.f || (gate && ((ldg & 7) || ((uintptr_t)gate & 15))))
     return mlxb_fail(MLXB_BAD_ARG, "attention (portions, tcgen05): %d kept positions, cap %g, gate rows at stride %d",
                      keep_first, (double)softcap, ldg);
@@ -461,7 +479,7 @@ MLXB_EXPORT int mlxb_attention_prefill_tc(const void* q, int ldq, int n_tokens, 
   if (int e = make_map(&mq, q, n_tokens, Hq * HD, ldq, TQ, "q")) return e;
   const long long pool_rows = (long long)n_pages * Hkv * page;
   if (int e = make_map(&mk, k_pool, pool_rows, HD, HD, page, "k pool")) return e;
-  if (int e = make_map(&mv, v_pool, pool_rows, HD, HD, page, "v pool")) return e;
+  if (int e = make_map(&mv, v_pool, (long long)n_pages * Hv * page, Dv, Dv, page, "v pool")) return e;
   const size_t smem = sizeof(AtSmem) + 1024;
   static bool raised = false;
   if (!raised) {
@@ -470,9 +488,9 @@ MLXB_EXPORT int mlxb_attention_prefill_tc(const void* q, int ldq, int n_tokens, 
       return mlxb_fail((int)e, "attention (portions, tcgen05): %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
     raised = true;
   }
-  launch_pdl(attention_prefill_tc_kernel, dim3(n_tiles, Hq), dim3(AT_THREADS), smem, stream, mq, mk, mv,
+  launch_pdl(attention_prefill_tc_kernel, dim3(n_tiles, Hq * VS), dim3(AT_THREADS), smem, stream, mq, mk, mv,
              (const int4*)tiles, block_table, max_pages, n_pages, page, Hq, Hkv, window,
              scale * 1.4426950408889634f, (__nv_bfloat16*)out, ldo, status, sinks, window > 0 ? keep_first : 0, softcap,
-             (const __nv_bfloat16*)gate, ldg);
+             (const __nv_bfloat16*)gate, ldg, Hv, VS, out_f32);
   return mlxb_check_launch("attention (portions, tcgen05)");
 }

@@ -525,7 +525,8 @@ PREFILL_TILE = int(_os.environ.get("MLXB_PREFILL_TILE", "128"))   # queries per 
 PREFILL_TC = _os.environ.get("MLXB_PREFILL_TC", "1") != "0"         # heads of 64 in tiles of 128 on the tcgen05 kernel
 
 _PRE_TC_ARGS = [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_float, c_void_p, c_int, c_void_p]
+                c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_float, c_void_p, c_int, c_int, c_int,
+                c_int, c_void_p]
 
 
 def attention_portions_supported(dtype, head_dim: int, scale: float = 1.0) -> bool:
@@ -534,10 +535,12 @@ def attention_portions_supported(dtype, head_dim: int, scale: float = 1.0) -> bo
 
 
 def attention_portions_tc_supported(q, out, k_pool, v_pool, tile_rows: int = 0) -> bool:
-    """Whether portions over these pools run on the tcgen05 kernel (``attention_portions``): bfloat16, key and value
-    heads of 64, tiles of 128 queries, pages that are a power of two from 8 to 128, rows in whole 16 bytes."""
+    """Whether portions over these pools run on the tcgen05 kernel (``attention_portions``): bfloat16, key heads of 64,
+    value rows of 64 columns or a multiple of it, value heads as many as the key heads or a divisor of them, tiles of
+    128 queries, pages that are a power of two from 8 to 128, rows in whole 16 bytes."""
     page, Dh = k_pool.shape[2], k_pool.shape[3]
-    return (PREFILL_TC and k_pool.dtype == torch.bfloat16 and Dh == 64 and v_pool is not None and v_pool.shape[3] == 64
+    return (PREFILL_TC and k_pool.dtype == torch.bfloat16 and Dh == 64 and v_pool is not None and v_pool.shape[3] % 64 == 0
+            and v_pool.shape[3] > 0 and v_pool.shape[1] > 0 and k_pool.shape[1] % v_pool.shape[1] == 0
             and (tile_rows or PREFILL_TILE) == 128 and 8 <= page <= 128 and page & (page - 1) == 0
             and _rows(q, "attention q") % 8 == 0 and _rows(out, "attention out") % 8 == 0
             and q.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0)
@@ -548,7 +551,9 @@ def attention_portions(q, tiles, n_tiles: int, block_table, k_pool, v_pool, out,
                        keep_first: int = 0, softcap: float = 0.0, gate=None) -> None:
     """Causal attention of prompt portions on tensor cores (bfloat16, csrc/attention_prefill.cu).
     ``keep_first``, ``softcap``, ``gate`` (bfloat16 ``[T, n_heads * 64]``, a sigmoid gate per output column): options of
-    the tcgen05 kernel only (``attention_portions_tc_supported``).
+    the tcgen05 kernel only (``attention_portions_tc_supported``).  So are a value pool with fewer heads than the key
+    pool (key heads ``c * Hkv/Hv ..`` read value head ``c``), value rows of a multiple of 64 columns (``out`` is then
+    ``[T, n_heads * value row]``) and a float32 ``out``.
 
     ``tiles``: int32 device tensor ``[n_tiles, 4]``: first token row of the tile, queries in it (1..64),
     block-table row of its request, position of its first query.  ``first_positions``: int32, per block-table
@@ -559,7 +564,18 @@ def attention_portions(q, tiles, n_tiles: int, block_table, k_pool, v_pool, out,
         if first_positions.numel() < block_table.shape[0]:
             raise KernelError(f"attention_portions: {first_positions.numel()} first positions for "
                               f"{block_table.shape[0]} requests")
-    n_pages, Hkv, page, Dh = _attn_shapes(q, out, k_pool, n_heads, "attention_portions")
+    Dv, Hv = v_pool.shape[3], v_pool.shape[1]
+    plain = Dv == k_pool.shape[3] and Hv == k_pool.shape[1] and out.dtype == k_pool.dtype
+    if plain:
+        n_pages, Hkv, page, Dh = _attn_shapes(q, out, k_pool, n_heads, "attention_portions")
+    else:
+        n_pages, Hkv, page, Dh = k_pool.shape
+        _need(q, k_pool.dtype, "attention_portions q")
+        if (q.shape[1] != n_heads * Dh or out.shape != (q.shape[0], n_heads * Dv) or out.dtype not in (k_pool.dtype, torch.float32)
+                or not attention_portions_tc_supported(q, out, k_pool, v_pool, tile_rows)):
+            raise KernelError(f"attention_portions: q {tuple(q.shape)}, out {out.dtype} {tuple(out.shape)}, pools "
+                              f"{tuple(k_pool.shape)} and {tuple(v_pool.shape)}: value heads or rows that differ from the "
+                              f"keys', and float32 results, are options of the tcgen05 kernel")
     _need(tiles, torch.int32, "attention_portions tiles")
     if tiles.numel() < 4 * n_tiles:
         raise KernelError(f"attention_portions: {tiles.numel()} integers for {n_tiles} tiles")
@@ -567,14 +583,14 @@ def attention_portions(q, tiles, n_tiles: int, block_table, k_pool, v_pool, out,
     ldq, ldo = _rows(q, "attention q"), _rows(out, "attention out")
     if gate is not None:
         _need(gate, torch.bfloat16, "attention_portions gate")
-        if gate.shape[0] != q.shape[0] or gate.shape[1] != n_heads * Dh:
+        if gate.shape[0] != q.shape[0] or gate.shape[1] != n_heads * Dv:
             raise KernelError(f"attention_portions: gate {tuple(gate.shape)} for {n_heads} heads of {Dh}")
     if attention_portions_tc_supported(q, out, k_pool, v_pool, tile_rows):
         _call("attention_prefill_tc", "mlxb_attention_prefill_tc", _PRE_TC_ARGS, _p(q), ldq, q.shape[0], _p(tiles),
               n_tiles, _p(block_table), block_table.shape[1], n_pages, page, n_heads, Hkv, Dh, window, scale,
               _p(k_pool), _p(v_pool), _p(out), ldo, _p(status), _sinks(sinks, n_heads, "attention_portions"),
               int(keep_first or 0), float(softcap or 0.0), _p(gate), _rows(gate, "attention gate") if gate is not None else 0,
-              stream)
+              Hv, Dv, int(out.dtype == torch.float32), stream)
         return
     if keep_first or softcap or gate is not None:
         raise KernelError("attention_portions: kept first positions, a cap and a gate are options of the tcgen05 kernel")
@@ -1076,14 +1092,15 @@ def attention_wide_step(ctx, q, q_head_stride: int, cache_k, cache_v, block_tabl
     """All of a step's rows through ``attention_wide``: on tensor cores where the sizes allow it (the portions' tiles
     and the single-token rows are two launches), else on the CUDA cores (float32 runs, odd sizes).  ``q_rounded``: the
     same queries in the pages' dtype, ``[T, n_heads * key_dim]``; with them the portions of plain heads of 64 (no score
-    mix, no runs of positions, a gate per column or none) go to the tcgen05 kernel of ``attention_portions``."""
+    mix, no runs of positions, a gate per column or none; values of 64 columns or a multiple, on as many heads as the
+    keys or a divisor of them) go to the tcgen05 kernel of ``attention_portions``."""
     if attention_wide_tc_supported(cache_k, cache_v, n_heads, key_dim, value_dim, talk is not None):
         if (ctx.n_portion and ctx.portion_tiles is not None and q_rounded is not None and talk is None and not chunk
-                and key_dim == 64 and value_dim == 64 and out_head_stride == 64 and scale > 0
-                and cache_v.shape[1] == cache_k.shape[1]
-                and (gate is None or gate.shape[1] == n_heads * value_dim)
+                and key_dim == 64 and value_dim % 64 == 0 and out_head_stride == value_dim and cache_v.shape[3] == value_dim
+                and scale > 0 and (gate is None or gate.shape[1] == n_heads * value_dim)
                 and (gate is None or (_rows(gate, "attention gate") % 8 == 0 and gate.data_ptr() % 16 == 0))
-                and out.dtype == cache_k.dtype and attention_portions_tc_supported(q_rounded, out, cache_k, cache_v)):
+                and out.dtype in (cache_k.dtype, torch.float32)
+                and attention_portions_tc_supported(q_rounded, out, cache_k, cache_v)):
             attention_portions(q_rounded, ctx.portion_tiles, ctx.n_portion_tiles, block_table, cache_k, cache_v, out,
                                n_heads, scale, window, ctx.status, ctx.stream, keep_first=keep_first, softcap=softcap,
                                gate=gate)

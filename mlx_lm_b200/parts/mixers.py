@@ -551,6 +551,9 @@ class DifferentialAttention(Mixer):
         self.out = Linear(f"{name}.o", n_heads * vdim, width, bias=False, weight_suffix="", init=init)
         self.lam = 0.0
         self.conv_w = self.conv_wt = self._no_state = None
+        if dim == 64 and vdim % 64 == 0:
+            # maps of 64 over values of 64 or a multiple: prompt portions run on the tcgen05 kernel
+            self.kernel_libs = type(self).kernel_libs + ("attention_prefill_tc", "elementwise")
 
     def children(self):
         return (self.proj, self.out)
@@ -625,12 +628,19 @@ class DifferentialAttention(Mixer):
                         self.eps, None, ctx.positions, ctx.token_req, kv.block_table, kv.k, kv.v, q, kv.write, ctx.status,
                         ctx.stream)
         maps = ctx.ws.get("attn_maps", T, 2 * H * self.vdim, torch.float32)
+        q_rounded = None
+        if (ctx.n_portion and ctx.portion_tiles is not None and "attention_prefill_tc" in self.kernel_libs
+                and x.dtype == torch.bfloat16 and kv.k.dtype == torch.bfloat16 and ops.PREFILL_TC):
+            # the tcgen05 kernel for portions takes the queries in bfloat16
+            q_rounded = ctx.ws.get("attn_q16", T, 2 * H * self.key_row, torch.bfloat16)
+            ops.label(self.name + ".prepare.cast", 0.0, 6.0 * T * 2 * H * self.key_row)
+            ops.join_rows(q, None, q_rounded, ctx.stream)
         if ops.recording():
             pairs, keys = visible_pairs(ctx, None, None)
             ops.label(self.name + ".maps.attention", pairs * 2 * H * (2.0 * self.dim + 2.0 * self.vdim),
                       es * keys * G * (2 * self.key_row + self.value_row) + 4.0 * T * 2 * H * (self.dim + self.vdim))
         ops.attention_wide_step(ctx, q, self.key_row, kv.k, kv.v, kv.block_table, maps, self.vdim, 2 * H, self.dim,
-                                self.vdim, self.scale)
+                                self.vdim, self.scale, q_rounded=q_rounded)
         o = ctx.ws.get("attn_out", T, H * self.vdim, x.dtype)
         ops.label(self.name + ".difference", 6.0 * T * H * self.vdim, (8.0 + es) * T * H * self.vdim)
         ops.head_difference(maps, H // G, self.vdim, self.lam, self.eps, 1.0 - self.diff, o, ctx.stream,

@@ -294,11 +294,13 @@ def test_queries_keys_and_values_on_their_way_to_the_pages(act, H, G, Hv, dk, dv
 
 
 @pytest.mark.parametrize("act", ACT)
-@pytest.mark.parametrize("H,G,dk,dv", [(4, 2, 32, 64), (6, 2, 16, 24), (3, 3, 6, 10), (8, 4, 64, 64), (3, 1, 48, 40)])
+@pytest.mark.parametrize("H,G,dk,dv", [(4, 2, 32, 64), (6, 2, 16, 24), (3, 3, 6, 10), (8, 4, 64, 64), (3, 1, 48, 40), (4, 2, 64, 128),
+                                       (6, 1, 64, 192)])
 def test_two_score_maps_over_the_same_values(act, H, G, dk, dv):
     """``2 H`` query heads in the kernels' order, ``2 G`` key heads, ``G`` value heads: every map is an attention of its
     own over its key/value head's values; then the difference of the maps, normed per head.  On the CUDA cores and,
-    in bfloat16, on tensor cores as portions and as single rows (whole, and split over CTAs)."""
+    in bfloat16, on tensor cores as portions and as single rows (whole, and split over CTAs); maps of 64 over values of
+    a multiple of 64 also on the tcgen05 kernel for portions (bfloat16 queries, float32 and bfloat16 results)."""
     from mlx_lm_b200 import ops
     torch.manual_seed(H + dk + dv)
     T, page, scale, lam, eps, post = 150, 16, 0.4, 0.37, 1e-5, 0.7
@@ -345,6 +347,23 @@ def test_two_score_maps_over_the_same_values(act, H, G, dk, dv):
         ops.attention_wide_tiles(qd, Dh, tiles, 3, 128, table.to(DEV), kp, vp, out2, dv, 2 * H, dk, dv, scale, status, stream())
         assert int(status.item()) == 0
         assert float((out2.double().cpu().view(T, 2 * H, dv) - maps).abs().max()) < tol
+        q16 = qd.to(torch.bfloat16)
+        if dk == 64 and dv % 64 == 0 and ops.attention_portions_tc_supported(q16, out2, kp, vp):
+            # the same queries rounded to bfloat16, as the tcgen05 kernel takes them
+            maps16 = torch.zeros(T, 2 * H, dv, dtype=torch.float64)
+            qr = q.to(torch.bfloat16).double()
+            for a in range(H):
+                c, r = a // rep, a % rep
+                for m in range(2):
+                    maps16[:, (2 * c + m) * rep + r] = plain.causal_softmax_values(qr[:, a, m], k[:, c, m].double(), v[:, c].double(), scale)
+            # (this kernel fetches whole blocks of 128 keys and multiplies the values of masked keys by zero: its pools
+            # are finite everywhere, as the engine's, which are zero-filled when they are made)
+            kz, vz = torch.nan_to_num(kp), torch.nan_to_num(vp)
+            for odt in (torch.float32, torch.bfloat16):
+                out4 = torch.full((T, 2 * H * dv), 7.0, dtype=odt, device=DEV)
+                ops.attention_portions(q16, tiles, 3, table.to(DEV), kz, vz, out4, 2 * H, scale, 0, status, stream())
+                assert int(status.item()) == 0
+                assert float((out4.double().cpu().view(T, 2 * H, dv) - maps16).abs().max()) < tol
         rows = [0, 1, 63, 64, 65, 127, 128, T - 1]
         singles = i32([[r, 1, 0, r] for r in rows] + [[5, 0, 0, 0]])
         for split in (False, True):
