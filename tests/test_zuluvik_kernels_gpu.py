@@ -23,7 +23,7 @@ def stream():
     return ops.current_stream()
 
 
-@pytest.mark.parametrize("outputs,identity,top,groups,scale", [(6, 2, 2, (3, 1), 1.5), (16, 4, 4, (4, 3), 1.5), (16, 0, 4, (4, 2), 1.0),
+@pytest.mark.parametrize("outputs,identity,top,groups,scale", [(6, 2, 2, (3, 1), 1.5), (16, 6, 4, (4, 3), 1.25), (16, 0, 4, (4, 2), 1.0),
                                                                 (70, 5, 6, (7, 3), 0.25), (5, 1, 3, None, 2.0), (9, 9, 2, (3, 2), 1.0),
                                                                 (12, 0, 12, (2, 2), 3.0), (64, 8, 8, (8, 1), 1.0)])
 def test_router_with_correction_groups_and_identity_experts(outputs, identity, top, groups, scale):

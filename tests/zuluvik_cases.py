@@ -75,9 +75,10 @@ _B = [two_maps(dim=48, heads=3, kv_heads=1, vdim=40, scale=0.15, diff=0.55, conv
       latent(dim=24, heads=6, rot_dim=16, vdim=8, kv_rank=72, scale=0.18, base=300.0,
              mlp=MOE(8, 0, 2, identity=4, groups=(2, 2), scale=0.5, shared=(64, 1.2)))]
 CONFIG_B = model(200, 96, [_B[0], again(_B, 0), _B[1], again(_B, 0)], scale=0.5, eps=1e-6)
-# W: sizes of a larger model's heads: eight heads of 64 over two key heads, latent rows of 128 + 32, sixteen experts
+# W: sizes of a larger model's heads: eight heads of 64 over two key heads, latent rows of 128 + 32, sixteen router
+# outputs and sixteen experts
 CONFIG_W = model(128, 128, [rotary(dim=64, heads=8, kv_heads=2, vdim=64, scale=0.125, rot_=rot(64, 50000.0, stretch(16.0, 128)),
-                                   mlp=MOE(64, 12, 4, identity=4, groups=(4, 2), scale=2.5, shared=(192, 2.0))),
+                                   mlp=MOE(96, 10, 4, identity=6, groups=(4, 2), scale=2.5, limit=2.5, shared=(192, 2.0))),
                             two_maps(dim=64, heads=8, kv_heads=4, vdim=64, scale=0.125, diff=0.2, conv=3, mlp=MOE(64, 16, 2)),
                             latent(dim=64, heads=8, rot_dim=32, vdim=64, kv_rank=128, scale=0.1, scaling=stretch(2.0, 256, 16.0, 2.0))],
                  scale=8.0)
