@@ -11,8 +11,6 @@
 
 MLXB_DEFINE_LAST_ERROR()
 
-__device__ __forceinline__ float silu_f(float v) { return v / (1.f + expf(-v)); }
-
 template <typename T>
 __global__ void gated_unit_kernel(const T* in, int ldi, T* __restrict__ out, int ldo, int F, int n, int act, float limit) {
   pdl_wait();
